@@ -1,0 +1,517 @@
+// extern "C" entry points of libxfold_b200.so: argument checking, tensor-map construction,
+// workspace carving and the launch sequences of the module-level operators.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "internal.h"
+
+namespace xf {
+
+struct AttnArgs;
+int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, int C, const float* g,
+                   const float* b, float eps, int H, const float* pw, float* proj, long long plane, const bf16* msc,
+                   const bf16* msh, int mod_rows, cudaStream_t st);
+int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, int ld, int R, int N, bf16* out, const float* gamma,
+                 const float* beta, float eps, cudaStream_t st);
+int launch_swiglu(Ctx* c, const bf16* in, bf16* out, long long rows, int F, cudaStream_t st);
+int launch_maskb(Ctx* c, const float* mask, long long mask_ld, float* out, int B, int S, int ld, cudaStream_t st);
+int launch_attention_op(Ctx* c, int D, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0,
+                        int k_col0, int v_col0, int g_col0, int head_groups, const float* bias,
+                        long long bias_head_stride, int bias_ld, const float* maskb, int maskb_ld, bf16* out,
+                        long long out_seq_stride, long long out_batch_stride, cudaStream_t st);
+
+int fail(Ctx* c, int code, const char* fmt, ...) {
+  if (c) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(c->last_error, sizeof(c->last_error), fmt, ap);
+    va_end(ap);
+  }
+  return code;
+}
+
+int check_launch(Ctx* c, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return XFOLD_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static bool load_encode() {
+  if (g_encode) return true;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) return false;
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return true;
+}
+
+bool make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
+                       uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2) {
+  if (!g_encode) return false;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1 * 2, s2 * 2};
+  cuuint32_t box[3] = {b0, b1, b2};
+  cuuint32_t es[3] = {1, 1, 1};
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (strides[0] & 15) || (strides[1] & 15)) return false;
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct Carver {
+  uint8_t* base;
+  size_t off = 0, cap;
+  Carver(void* p, size_t n) : base(static_cast<uint8_t*>(p)), cap(n) {}
+  void* take(size_t bytes) {
+    off = align_up(off, 1024);
+    void* r = base ? base + off : nullptr;
+    off += bytes;
+    return r;
+  }
+  bool ok() const { return off <= cap; }
+};
+
+// ---------------------------------------------------------------------------------------------
+// generic linear layers on top of the GEMM kernel
+// ---------------------------------------------------------------------------------------------
+static int gemm_rows(Ctx* c, int epi, const bf16* x, long long ldx, long long M, int K, const bf16* w, int wrows, int ldw,
+                     GemmArgs a, int bn, cudaStream_t st) {
+  if (M <= 0) return XFOLD_OK;
+  if ((K & 7) || (ldx & 7) || (ldw & 7)) return fail(c, XFOLD_ERR_ARG, "linear: K and leading dimensions must be multiples of 8");
+  CUtensorMap tA, tB;
+  if (!make_tmap_bf16_3d(&tA, x, K, M, 1, ldx, (uint64_t)ldx * M, 64, 128, 1))
+    return fail(c, XFOLD_ERR_ARG, "linear: cannot encode the activation tensor map (base 16 B aligned?)");
+  if (!make_tmap_bf16_3d(&tB, w, K, wrows, 1, ldw, (uint64_t)ldw * wrows, 64, bn, 1))
+    return fail(c, XFOLD_ERR_ARG, "linear: cannot encode the weight tensor map");
+  a.M = (int)M;
+  a.K = K;
+  a.batches = 1;
+  a.tiles_m = (int)((M + 127) / 128);
+  a.status = c->d_status;
+  return launch_gemm(c, epi, bn, tA, tB, a, st);
+}
+
+static int linear_plain(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N, const float* bias,
+                        const float* scale, bf16* out, long long ldo, cudaStream_t st) {
+  if (M >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "linear: too many rows");
+  GemmArgs a;
+  const int bn = (N > 128) ? 256 : 128;
+  a.N = N;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.out = out;
+  a.ldo = ldo;
+  a.col_bias = bias;
+  a.col_scale = scale;
+  return gemm_rows(c, EPI_PLAIN, x, ldx, M, K, w, N, K, a, bn, st);
+}
+
+static int linear_gate_resid(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N,
+                             const bf16* gate, long long ldg, int row_gate_mod, const bf16* resid, long long ldr,
+                             bf16* out, long long ldo, cudaStream_t st) {
+  if (M >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "linear: too many rows");
+  GemmArgs a;
+  const int bn = 128;
+  a.N = N;
+  a.tiles_n = (N + bn - 1) / bn;
+  a.out = out;
+  a.ldo = ldo;
+  if (row_gate_mod > 0) { a.row_gate = gate; a.row_gate_mod = row_gate_mod; }
+  else a.gate = gate;
+  a.ldg = ldg;
+  a.resid = resid;
+  a.ldr = ldr;
+  return gemm_rows(c, EPI_GATE_RESID, x, ldx, M, K, w, N, K, a, bn, st);
+}
+
+static int linear_swiglu(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* wp, int F, bf16* out,
+                         long long ldo, cudaStream_t st) {
+  if (F % 128) return fail(c, XFOLD_ERR_ARG, "linear_swiglu: F must be a multiple of 128");
+  if (M >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "linear: too many rows");
+  GemmArgs a;
+  a.N = 2 * F;
+  a.tiles_n = F / 128;
+  a.out = out;
+  a.ldo = ldo;
+  return gemm_rows(c, EPI_SWIGLU, x, ldx, M, K, wp, 2 * F, K, a, 256, st);
+}
+
+static int batched_contract(Ctx* c, const bf16* a_, const bf16* b_, bf16* out, int channels, int Mi, int Nj, int Kk,
+                            long long ld, long long csa, long long csb, long long ldo, long long cso, cudaStream_t st) {
+  if ((ld & 7) || (csa & 7) || (csb & 7) || (ldo & 7) || (cso & 7))
+    return fail(c, XFOLD_ERR_ARG, "contract: strides must be multiples of 8 elements");
+  CUtensorMap tA, tB;
+  if (!make_tmap_bf16_3d(&tA, a_, Kk, Mi, channels, ld, csa, 64, 128, 1) ||
+      !make_tmap_bf16_3d(&tB, b_, Kk, Nj, channels, ld, csb, 64, 256, 1))
+    return fail(c, XFOLD_ERR_ARG, "contract: cannot encode tensor maps");
+  GemmArgs a;
+  a.M = Mi;
+  a.N = Nj;
+  a.K = Kk;
+  a.batches = channels;
+  a.b_batched = 1;
+  a.tiles_m = (Mi + 127) / 128;
+  a.tiles_n = (Nj + 255) / 256;
+  a.out = out;
+  a.ldo = ldo;
+  a.out_batch_stride = cso;
+  a.status = c->d_status;
+  return launch_gemm(c, EPI_PLAIN, 256, tA, tB, a, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// module-level operators
+// ---------------------------------------------------------------------------------------------
+static inline int pad8(int n) { return (n + 7) & ~7; }
+
+struct TriMulWs {
+  bf16 *x, *a, *b, *g, *o;
+  int ld;
+  size_t bytes;
+};
+static TriMulWs carve_trimul(void* ws, size_t cap, int N) {
+  TriMulWs w;
+  Carver cv(ws, cap);
+  w.ld = pad8(N);
+  const size_t tok = (size_t)N * N * 128 * 2;
+  const size_t cm = (size_t)128 * N * w.ld * 2;
+  w.x = (bf16*)cv.take(tok);
+  w.g = (bf16*)cv.take(tok);
+  w.a = (bf16*)cv.take(cm);
+  w.b = (bf16*)cv.take(cm);
+  w.o = (bf16*)cv.take(cm);
+  w.bytes = cv.off;
+  return w;
+}
+
+static int trimul_fwd(Ctx* c, bf16* z, const float* mask, int N, int outgoing, const xfold_trimul_weights* w, void* ws,
+                      size_t ws_bytes, cudaStream_t st) {
+  if (!z || !w || !w->w_in || !w->w_out) return fail(c, XFOLD_ERR_ARG, "trimul: null argument");
+  if (N <= 0) return XFOLD_OK;
+  TriMulWs W = carve_trimul(ws, ws_bytes, N);
+  if (!ws || W.bytes > ws_bytes) return fail(c, XFOLD_ERR_ARG, "trimul: workspace too small (%zu < %zu)", ws_bytes, W.bytes);
+  const long long M = (long long)N * N;
+  int rc = launch_ln_rows(c, z, 128, W.x, 128, M, 128, w->ln_in_gamma, w->ln_in_beta, 1e-5f, 0, nullptr, nullptr, 0,
+                          nullptr, nullptr, 0, st);
+  if (rc) return rc;
+  // gated projections -> a, b channel-major (incoming: stored transposed), gating_linear -> g token-major
+  {
+    CUtensorMap tA, tB;
+    bool ok;
+    GemmArgs a;
+    if (outgoing) {
+      ok = make_tmap_bf16_3d(&tA, W.x, 128, M, 1, 128, (uint64_t)128 * M, 64, 128, 1);
+      a.a_row_mode = 0;
+      a.tiles_m = (int)((M + 127) / 128);
+    } else {
+      ok = make_tmap_bf16_3d(&tA, W.x, 128, N, N, 128, (uint64_t)128 * N, 64, 1, 128);
+      a.a_row_mode = 1;
+      a.a_dim1 = N;
+      a.tiles_m = N * ((N + 127) / 128);
+    }
+    ok = ok && make_tmap_bf16_3d(&tB, w->w_in, 128, 640, 1, 128, 128 * 640, 64, 256, 1);
+    if (!ok) return fail(c, XFOLD_ERR_ARG, "trimul: cannot encode projection tensor maps");
+    a.M = (int)M;
+    a.N = 640;
+    a.K = 128;
+    a.tiles_n = 3;
+    a.out_a = W.a;
+    a.out_b = W.b;
+    a.out_g = W.g;
+    a.cm_chan_stride = (long long)N * W.ld;
+    a.cm_ld = W.ld;
+    a.ntok = N;
+    a.mask = mask;
+    a.status = c->d_status;
+    rc = launch_gemm(c, EPI_TRIMUL_AB, 256, tA, tB, a, st);
+    if (rc) return rc;
+  }
+  // contraction: outgoing o[c][i][j] = sum_k a[c][i][k] b[c][j][k]; incoming uses the transposed stores:
+  // o[c][i][j] = sum_k bT[c][i][k] aT[c][j][k]
+  const long long cs = (long long)N * W.ld;
+  rc = batched_contract(c, outgoing ? W.a : W.b, outgoing ? W.b : W.a, W.o, 128, N, N, N, W.ld, cs, cs, W.ld, cs, st);
+  if (rc) return rc;
+  rc = launch_cm_ln(c, W.o, cs, W.ld, N, N, W.x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
+  if (rc) return rc;
+  return linear_gate_resid(c, W.x, 128, M, 128, (const bf16*)w->w_out, 128, W.g, 128, 0, z, 128, z, 128, st);
+}
+
+struct TriAttnWs {
+  bf16 *x, *qkvg;
+  float *nb, *maskb;
+  int ldm;
+  size_t bytes;
+};
+static TriAttnWs carve_triattn(void* ws, size_t cap, int N) {
+  TriAttnWs w;
+  Carver cv(ws, cap);
+  w.ldm = (N + 127) / 128 * 128;
+  w.x = (bf16*)cv.take((size_t)N * N * 128 * 2);
+  w.qkvg = (bf16*)cv.take((size_t)N * N * 512 * 2);
+  w.nb = (float*)cv.take((size_t)4 * N * N * 4);
+  w.maskb = (float*)cv.take((size_t)N * w.ldm * 4);
+  w.bytes = cv.off;
+  return w;
+}
+
+static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose, const xfold_triattn_weights* w, void* ws,
+                       size_t ws_bytes, cudaStream_t st) {
+  if (!z || !w || !w->w_qkvg || !w->w_out || !w->w_bias) return fail(c, XFOLD_ERR_ARG, "triattn: null argument");
+  if (N <= 0) return XFOLD_OK;
+  TriAttnWs W = carve_triattn(ws, ws_bytes, N);
+  if (!ws || W.bytes > ws_bytes) return fail(c, XFOLD_ERR_ARG, "triattn: workspace too small (%zu < %zu)", ws_bytes, W.bytes);
+  const long long M = (long long)N * N;
+  int rc = launch_ln_rows(c, z, 128, W.x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, W.nb, M, nullptr,
+                          nullptr, 0, st);
+  if (rc) return rc;
+  rc = linear_plain(c, W.x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, W.qkvg, 512, st);
+  if (rc) return rc;
+  rc = launch_maskb(c, mask, N, W.maskb, N, N, W.ldm, st);
+  if (rc) return rc;
+  // attention output (gated) goes to W.x, which is dead after the projection
+  const long long seq_stride = transpose ? (long long)N * 128 : 128;
+  const long long batch_stride = transpose ? 128 : (long long)N * 128;
+  rc = launch_attention_op(c, 32, W.qkvg, 512, N, N, transpose, 0, 128, 256, 384, 1, W.nb, M, N, W.maskb, W.ldm, W.x,
+                           seq_stride, batch_stride, st);
+  if (rc) return rc;
+  return linear_gate_resid(c, W.x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, z, 128, z, 128, st);
+}
+
+static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
+                          size_t ws_bytes, cudaStream_t st) {
+  if (!x || !w || !w->w1_packed || !w->w2) return fail(c, XFOLD_ERR_ARG, "transition: null argument");
+  if (rows <= 0) return XFOLD_OK;
+  Carver cv(ws, ws_bytes);
+  bf16* xn = (bf16*)cv.take((size_t)rows * C * 2);
+  bf16* h = (bf16*)cv.take((size_t)rows * F * 2);
+  if (!ws || !cv.ok()) return fail(c, XFOLD_ERR_ARG, "transition: workspace too small (%zu < %zu)", ws_bytes, cv.off);
+  int rc = launch_ln_rows(c, x, C, xn, C, rows, C, w->ln_gamma, w->ln_beta, 1e-5f, 0, nullptr, nullptr, 0, nullptr,
+                          nullptr, 0, st);
+  if (rc) return rc;
+  rc = linear_swiglu(c, xn, C, rows, C, (const bf16*)w->w1_packed, F, h, F, st);
+  if (rc) return rc;
+  return linear_gate_resid(c, h, F, rows, F, (const bf16*)w->w2, C, nullptr, 0, 0, x, C, x, C, st);
+}
+
+static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, bf16** qkvg, float** maskb, int* ldm) {
+  Carver local(nullptr, 0);
+  if (!cv) cv = &local;
+  const int l = (S + 127) / 128 * 128;
+  bf16* q = (bf16*)cv->take((size_t)B * S * 4 * H * Dp * 2);
+  float* m = (float*)cv->take((size_t)l * 4);
+  if (qkvg) *qkvg = q;
+  if (maskb) *maskb = m;
+  if (ldm) *ldm = l;
+  return cv->off;
+}
+
+static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
+                        const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const float* mask,
+                        bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (!xn || !w_qkvg || !out || !pair_bias) return fail(c, XFOLD_ERR_ARG, "apb: null argument");
+  if ((Dp != 32 && Dp != 64) || (H * Dp) % 128) return fail(c, XFOLD_ERR_ARG, "apb: H x Dp must be a multiple of 128 with Dp 32 or 64");
+  Carver cv(ws, ws_bytes);
+  bf16* qkvg;
+  float* maskb;
+  int ldm;
+  apb_ws(B, S, H, Dp, &cv, &qkvg, &maskb, &ldm);
+  if (!ws || !cv.ok()) return fail(c, XFOLD_ERR_ARG, "apb: workspace too small (%zu < %zu)", ws_bytes, cv.off);
+  const int Wd = H * Dp;
+  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, qkvg, 4 * Wd, st);
+  if (rc) return rc;
+  rc = launch_maskb(c, mask, 0, maskb, 1, S, ldm, st);
+  if (rc) return rc;
+  return launch_attention_op(c, Dp, qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, Wd / 128, pair_bias, (long long)S * S, S,
+                             maskb, 0, out, Wd, (long long)S * Wd, st);
+}
+
+static size_t pairformer_ws_bytes(int N) {
+  size_t a = carve_trimul(nullptr, 0, N).bytes;
+  size_t b = carve_triattn(nullptr, 0, N).bytes;
+  size_t t = align_up((size_t)N * N * 128 * 2, 1024) + align_up((size_t)N * N * 512 * 2, 1024) + 2048;
+  size_t m = a > b ? a : b;
+  if (t > m) m = t;
+  // single path: pair logits [16][N][N] fp32 + xn [N][384] + attention scratch + o [N][512] + transition scratch
+  size_t s = align_up((size_t)16 * N * N * 4, 1024) + align_up((size_t)N * 384 * 2, 1024) + apb_ws(1, N, 16, 32, nullptr, nullptr, nullptr, nullptr) +
+             align_up((size_t)N * 512 * 2, 1024) + align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 8192;
+  return (m > s ? m : s) + 4096;
+}
+
+static int pairformer_fwd(Ctx* c, bf16* z, bf16* s, const float* pair_mask, const float* seq_mask, int N,
+                          const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (!z || !w) return fail(c, XFOLD_ERR_ARG, "pairformer: null argument");
+  if (ws_bytes < pairformer_ws_bytes(N)) return fail(c, XFOLD_ERR_ARG, "pairformer: workspace too small (%zu < %zu)", ws_bytes, pairformer_ws_bytes(N));
+  int rc;
+  if ((rc = trimul_fwd(c, z, pair_mask, N, 1, &w->tri_out, ws, ws_bytes, st))) return rc;
+  if ((rc = trimul_fwd(c, z, pair_mask, N, 0, &w->tri_in, ws, ws_bytes, st))) return rc;
+  if ((rc = triattn_fwd(c, z, pair_mask, N, 0, &w->att_start, ws, ws_bytes, st))) return rc;
+  if ((rc = triattn_fwd(c, z, pair_mask, N, 1, &w->att_end, ws, ws_bytes, st))) return rc;
+  if ((rc = transition_fwd(c, z, (long long)N * N, 128, 512, &w->pair_transition, ws, ws_bytes, st))) return rc;
+  if (!s || !w->spl_w) return XFOLD_OK;
+  Carver cv(ws, ws_bytes);
+  float* pl = (float*)cv.take((size_t)16 * N * N * 4);
+  bf16* xn = (bf16*)cv.take((size_t)N * 384 * 2);
+  bf16* o = (bf16*)cv.take((size_t)N * 512 * 2);
+  const size_t apb_bytes = apb_ws(1, N, 16, 32, nullptr, nullptr, nullptr, nullptr);
+  void* apb_scratch = cv.take(apb_bytes);
+  const size_t tr_bytes = align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 2048;
+  void* tr_scratch = cv.take(tr_bytes);
+  if (!cv.ok()) return fail(c, XFOLD_ERR_ARG, "pairformer: workspace too small for the single path");
+  const long long M = (long long)N * N;
+  if ((rc = launch_ln_rows(c, z, 128, nullptr, 128, M, 128, w->spl_ln_gamma, w->spl_ln_beta, 1e-5f, 16, w->spl_w, pl, M,
+                           nullptr, nullptr, 0, st))) return rc;
+  if ((rc = launch_ln_rows(c, s, 384, xn, 384, N, 384, w->sa_ln_gamma, w->sa_ln_beta, 1e-5f, 0, nullptr, nullptr, 0,
+                           nullptr, nullptr, 0, st))) return rc;
+  if ((rc = apb_core_fwd(c, xn, 1, N, 384, 16, 32, (const bf16*)w->sa_w_qkvg, w->sa_qkvg_bias, w->sa_qkvg_scale, pl,
+                         seq_mask, o, apb_scratch, apb_bytes, st))) return rc;
+  if ((rc = linear_gate_resid(c, o, 512, N, 512, (const bf16*)w->sa_w_out, 384, nullptr, 0, 0, s, 384, s, 384, st))) return rc;
+  return transition_fwd(c, s, N, 384, 1536, &w->single_transition, tr_scratch, tr_bytes, st);
+}
+
+}  // namespace xf
+
+using namespace xf;
+
+struct xfold_ctx : public xf::Ctx {};
+
+extern "C" {
+
+const char* xfold_version(void) { return "xfold_b200 0.1 (sm_100a, tcgen05/TMA)"; }
+
+int xfold_ctx_create(int device, xfold_ctx** out) {
+  if (!out) return XFOLD_ERR_ARG;
+  *out = nullptr;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) return XFOLD_ERR_DEVICE;
+  if (cudaSetDevice(device) != cudaSuccess) return XFOLD_ERR_DEVICE;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return XFOLD_ERR_DEVICE;
+  if (prop.major != 10) return XFOLD_ERR_DEVICE;  // sm_100a code only
+  if (!load_encode()) return XFOLD_ERR_DEVICE;
+  xfold_ctx* c = new xfold_ctx();
+  c->device = device;
+  c->sm_count = prop.multiProcessorCount;
+  if (cudaMalloc(&c->d_status, sizeof(int)) != cudaSuccess) { delete c; return XFOLD_ERR_DEVICE; }
+  cudaMemset(c->d_status, 0, sizeof(int));
+  *out = c;
+  return XFOLD_OK;
+}
+
+void xfold_ctx_destroy(xfold_ctx* c) {
+  if (!c) return;
+  if (c->d_status) cudaFree(c->d_status);
+  delete c;
+}
+
+const char* xfold_last_error(xfold_ctx* c) { return c ? c->last_error : "null context"; }
+
+int xfold_check_status(xfold_ctx* c, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  int h = 0;
+  cudaError_t e = cudaMemcpyAsync(&h, c->d_status, sizeof(int), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "status read: %s", cudaGetErrorString(e));
+  if (h != 0) {
+    cudaMemsetAsync(c->d_status, 0, sizeof(int), st);
+    cudaStreamSynchronize(st);
+    return fail(c, XFOLD_ERR_TIMEOUT, "in-kernel bounded wait ran out (code %d)", h);
+  }
+  return XFOLD_OK;
+}
+
+int xfold_layernorm_fwd(xfold_ctx* c, const void* x, long long ldx, void* y, long long ldy, long long rows, int C,
+                        const float* gamma, const float* beta, float eps, int num_proj, const float* proj_w,
+                        float* proj, long long proj_plane, const void* mod_scale, const void* mod_shift, int mod_rows,
+                        void* stream) {
+  if (!c || !x) return XFOLD_ERR_ARG;
+  if (num_proj > 0 && (!proj_w || !proj)) return fail(c, XFOLD_ERR_ARG, "layernorm: projection requested without buffers");
+  if ((mod_scale != nullptr) != (mod_shift != nullptr) || (mod_scale && mod_rows <= 0))
+    return fail(c, XFOLD_ERR_ARG, "layernorm: modulation needs scale, shift and mod_rows");
+  return launch_ln_rows(c, (const bf16*)x, ldx, (bf16*)y, ldy, rows, C, gamma, beta, eps, num_proj, proj_w, proj,
+                        proj_plane, (const bf16*)mod_scale, (const bf16*)mod_shift, mod_rows, (cudaStream_t)stream);
+}
+
+int xfold_swiglu_fwd(xfold_ctx* c, const void* in, void* out, long long rows, int F, void* stream) {
+  if (!c || !in || !out) return XFOLD_ERR_ARG;
+  return launch_swiglu(c, (const bf16*)in, (bf16*)out, rows, F, (cudaStream_t)stream);
+}
+
+int xfold_linear_fwd(xfold_ctx* c, const void* x, long long ldx, long long M, int K, const void* w, int N,
+                     const float* bias, const float* scale, void* out, long long ldo, void* stream) {
+  if (!c || !x || !w || !out) return XFOLD_ERR_ARG;
+  return linear_plain(c, (const bf16*)x, ldx, M, K, (const bf16*)w, N, bias, scale, (bf16*)out, ldo, (cudaStream_t)stream);
+}
+
+int xfold_linear_gate_residual_fwd(xfold_ctx* c, const void* x, long long ldx, long long M, int K, const void* w, int N,
+                                   const void* gate, long long ldg, int row_gate_mod, const void* resid, long long ldr,
+                                   void* out, long long ldo, void* stream) {
+  if (!c || !x || !w || !out) return XFOLD_ERR_ARG;
+  return linear_gate_resid(c, (const bf16*)x, ldx, M, K, (const bf16*)w, N, (const bf16*)gate, ldg, row_gate_mod,
+                           (const bf16*)resid, ldr, (bf16*)out, ldo, (cudaStream_t)stream);
+}
+
+int xfold_linear_swiglu_fwd(xfold_ctx* c, const void* x, long long ldx, long long M, int K, const void* w_packed, int F,
+                            void* out, long long ldo, void* stream) {
+  if (!c || !x || !w_packed || !out) return XFOLD_ERR_ARG;
+  return linear_swiglu(c, (const bf16*)x, ldx, M, K, (const bf16*)w_packed, F, (bf16*)out, ldo, (cudaStream_t)stream);
+}
+
+int xfold_batched_contract_fwd(xfold_ctx* c, const void* a, const void* b, void* out, int channels, int Mi, int Nj, int Kk,
+                               long long ld, long long chan_stride_a, long long chan_stride_b, long long ldo,
+                               long long chan_stride_o, void* stream) {
+  if (!c || !a || !b || !out) return XFOLD_ERR_ARG;
+  return batched_contract(c, (const bf16*)a, (const bf16*)b, (bf16*)out, channels, Mi, Nj, Kk, ld, chan_stride_a,
+                          chan_stride_b, ldo, chan_stride_o, (cudaStream_t)stream);
+}
+
+size_t xfold_trimul_workspace_bytes(int N) { return carve_trimul(nullptr, 0, N).bytes; }
+int xfold_triangle_multiplication_fwd(xfold_ctx* c, void* z, const float* mask, int N, int outgoing,
+                                      const xfold_trimul_weights* w, void* ws, size_t ws_bytes, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return trimul_fwd(c, (bf16*)z, mask, N, outgoing, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+size_t xfold_triattn_workspace_bytes(int N) { return carve_triattn(nullptr, 0, N).bytes; }
+int xfold_triangle_attention_fwd(xfold_ctx* c, void* z, const float* mask, int N, int transpose,
+                                 const xfold_triattn_weights* w, void* ws, size_t ws_bytes, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return triattn_fwd(c, (bf16*)z, mask, N, transpose, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+size_t xfold_transition_workspace_bytes(long long rows, int C, int F) {
+  return align_up((size_t)rows * C * 2, 1024) + align_up((size_t)rows * F * 2, 1024) + 2048;
+}
+int xfold_transition_fwd(xfold_ctx* c, void* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
+                         size_t ws_bytes, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return transition_fwd(c, (bf16*)x, rows, C, F, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+size_t xfold_apb_workspace_bytes(int B, int S, int H, int Dp) { return apb_ws(B, S, H, Dp, nullptr, nullptr, nullptr, nullptr) + 2048; }
+int xfold_attention_pair_bias_core_fwd(xfold_ctx* c, const void* xn, int B, int S, int C, int H, int Dp,
+                                       const void* w_qkvg, const float* qkvg_bias, const float* qkvg_scale,
+                                       const float* pair_bias, const float* mask, void* out, void* ws, size_t ws_bytes,
+                                       void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return apb_core_fwd(c, (const bf16*)xn, B, S, C, H, Dp, (const bf16*)w_qkvg, qkvg_bias, qkvg_scale, pair_bias, mask,
+                      (bf16*)out, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+size_t xfold_pairformer_workspace_bytes(int N) { return pairformer_ws_bytes(N); }
+int xfold_pairformer_block_fwd(xfold_ctx* c, void* z, void* s, const float* pair_mask, const float* seq_mask, int N,
+                               const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return pairformer_fwd(c, (bf16*)z, (bf16*)s, pair_mask, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,66 @@
+// Host-side declarations shared by the translation units of libxfold_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/xfold_b200.h"
+
+namespace xf {
+
+typedef __nv_bfloat16 bf16;
+
+struct Ctx {
+  int device = 0;
+  int sm_count = 148;
+  int* d_status = nullptr;  // one word: first in-kernel error code (0 = ok)
+  char last_error[256] = {0};
+};
+
+// returns XFOLD_OK or sets ctx->last_error and returns a status code
+int fail(Ctx* c, int code, const char* fmt, ...);
+int check_launch(Ctx* c, const char* what);
+
+// ---- tensor maps --------------------------------------------------------------------------
+// bf16 tensor of rank 3, innermost stride 1; s1/s2 are strides of dims 1/2 in ELEMENTS.
+// 128-byte swizzle, zero fill outside the extents.
+bool make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
+                       uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2);
+
+// ---- GEMM ---------------------------------------------------------------------------------
+enum GemmEpi : int { EPI_PLAIN = 0, EPI_GATE_RESID = 1, EPI_SWIGLU = 2, EPI_TRIMUL_AB = 3 };
+
+struct GemmArgs {
+  int M = 0, N = 0, K = 0, batches = 1;
+  int tiles_m = 0, tiles_n = 0;
+  int a_row_mode = 0;  // 0: tile rows are consecutive rows of A; 1: tile rows step along dim 2, dim 1 fixed
+  int a_dim1 = 1;      // row mode 1: extent of dim 1
+  int b_batched = 0;
+  // PLAIN / SWIGLU / GATE_RESID output
+  bf16* out = nullptr;
+  long long ldo = 0, out_batch_stride = 0;
+  const float* col_bias = nullptr;
+  const float* col_scale = nullptr;
+  const bf16* resid = nullptr;
+  long long ldr = 0;
+  const bf16* gate = nullptr;
+  long long ldg = 0;
+  const bf16* row_gate = nullptr;  // GATE_RESID: gate indexed by (m % row_gate_mod), for conditioning shared by samples
+  int row_gate_mod = 0;
+  // TRIMUL_AB
+  bf16* out_a = nullptr;
+  bf16* out_b = nullptr;
+  bf16* out_g = nullptr;
+  long long cm_chan_stride = 0;
+  int cm_ld = 0;
+  int ntok = 0;
+  const float* mask = nullptr;
+  int* status = nullptr;
+};
+
+// A is described by tmA (box 64 x 128 rows), B by tmB (box 64 x BN rows); BN is 128 or 256.
+int launch_gemm(Ctx* c, int epi, int bn, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& a,
+                cudaStream_t st);
+
+}  // namespace xf

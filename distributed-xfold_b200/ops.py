@@ -1,0 +1,354 @@
+"""Torch-facing wrappers of the C ABI: weight packing (the counterpart of the reference's
+``load_xsmm_params`` methods) and one Python function per fused operator (the counterpart of
+``xsmm_kernels/prototypes/*.py``).  Tensors must live on an sm_100 GPU; nothing here computes on
+the CPU and nothing falls back to eager PyTorch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional
+
+import torch
+
+from . import _cabi
+from ._cabi import (PairformerWeights, TransitionWeights, TriAttnWeights, TriMulWeights, check, ctx, load)
+
+State = Dict[str, torch.Tensor]
+BF16 = torch.bfloat16
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise _cabi.XfoldError("xfold_b200 operators run on a B200 GPU only: got a CPU tensor (no CPU fallback)")
+
+
+def _dev(t: torch.Tensor) -> int:
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+class _Workspace:
+    """Grow-only scratch buffer per device, reused by every operator call on that device."""
+    _bufs: Dict[int, torch.Tensor] = {}
+
+    @classmethod
+    def get(cls, device: int, nbytes: int) -> torch.Tensor:
+        b = cls._bufs.get(device)
+        if b is None or b.numel() < nbytes:
+            cls._bufs[device] = None
+            b = torch.empty(int(nbytes), dtype=torch.uint8, device=f"cuda:{device}")
+            cls._bufs[device] = b
+        return b
+
+
+def synchronize_and_check(device: Optional[int] = None) -> None:
+    """Synchronises the current stream and raises if a kernel reported a bounded-wait time-out."""
+    device = torch.cuda.current_device() if device is None else device
+    rc = load().xfold_check_status(ctx(device), _stream(device))
+    check(rc, device, "xfold_check_status")
+
+
+# ---------------------------------------------------------------------------------------------
+# weight packing
+# ---------------------------------------------------------------------------------------------
+def _f32(t, device):
+    return None if t is None else t.detach().to(device=device, dtype=torch.float32).contiguous()
+
+
+def _b16(t, device):
+    return t.detach().to(device=device, dtype=BF16).contiguous()
+
+
+class PackedTriMul:
+    """De-interleaves a/b (even/odd rows, nn/d_triangle_multiplication.py:128-129) and stacks
+    projection, gate and gating_linear into one [640, 128] matrix."""
+
+    def __init__(self, state: State, prefix: str, device):
+        p, g = state[prefix + "projection.weight"], state[prefix + "gate.weight"]
+        w_in = torch.cat([p[0::2], g[0::2], p[1::2], g[1::2], state[prefix + "gating_linear.weight"]], 0)
+        self.w_in = _b16(w_in, device)
+        self.w_out = _b16(state[prefix + "output_projection.weight"], device)
+        self.ln_in_g = _f32(state.get(prefix + "left_norm_input.weight"), device)
+        self.ln_in_b = _f32(state.get(prefix + "left_norm_input.bias"), device)
+        self.ln_c_g = _f32(state.get(prefix + "center_norm.weight"), device)
+        self.ln_c_b = _f32(state.get(prefix + "center_norm.bias"), device)
+        self.c = TriMulWeights(_ptr(self.ln_in_g), _ptr(self.ln_in_b), _ptr(self.w_in), _ptr(self.ln_c_g),
+                               _ptr(self.ln_c_b), _ptr(self.w_out))
+
+
+class PackedTriAttn:
+    def __init__(self, state: State, prefix: str, device, num_head: int = 4):
+        c = state[prefix + "q_projection.weight"].shape[0]
+        d = c // num_head
+        w = torch.cat([state[prefix + n + ".weight"] for n in ("q_projection", "k_projection", "v_projection",
+                                                               "gating_query")], 0)
+        self.w_qkvg = _b16(w, device)
+        scale = torch.ones(4 * c)
+        scale[:c] = d ** -0.5
+        self.scale = _f32(scale, device)
+        self.w_bias = _f32(state[prefix + "pair_bias_projection.weight"], device)
+        self.w_out = _b16(state[prefix + "output_projection.weight"], device)
+        self.ln_g = _f32(state.get(prefix + "act_norm.weight"), device)
+        self.ln_b = _f32(state.get(prefix + "act_norm.bias"), device)
+        self.c = TriAttnWeights(_ptr(self.ln_g), _ptr(self.ln_b), _ptr(self.w_bias), _ptr(self.w_qkvg),
+                                _ptr(self.scale), _ptr(self.w_out))
+
+
+def pack_swiglu_weight(w1: torch.Tensor) -> torch.Tensor:
+    """[2F, C] (rows 0..F-1 feed SiLU, rows F..2F-1 are the linear half, kernel_test/transition.py:40-42)
+    -> 256-row tiles [128 SiLU rows | 128 linear rows] so both halves of an output meet in one tile."""
+    f = w1.shape[0] // 2
+    assert f % 128 == 0
+    a, b = w1[:f].reshape(f // 128, 128, -1), w1[f:].reshape(f // 128, 128, -1)
+    return torch.cat([a, b], 1).reshape(2 * f, -1)
+
+
+class PackedTransition:
+    def __init__(self, state: State, prefix: str, device):
+        w1 = state[prefix + "transition1.weight"]
+        self.C = w1.shape[1]
+        self.F = w1.shape[0] // 2
+        self.w1 = _b16(pack_swiglu_weight(w1), device)
+        self.w2 = _b16(state[prefix + "transition2.weight"], device)
+        self.ln_g = _f32(state.get(prefix + "input_layer_norm.weight"), device)
+        self.ln_b = _f32(state.get(prefix + "input_layer_norm.bias"), device)
+        self.c = TransitionWeights(_ptr(self.ln_g), _ptr(self.ln_b), _ptr(self.w1), _ptr(self.w2))
+
+
+def _pad_heads_rows(w: torch.Tensor, num_head: int, dp: int) -> torch.Tensor:
+    """[H*d, C] -> [H*dp, C] with zero rows after each head's d rows."""
+    hd, cdim = w.shape
+    d = hd // num_head
+    out = torch.zeros(num_head, dp, cdim, dtype=w.dtype)
+    out[:, :d] = w.reshape(num_head, d, cdim).cpu()
+    return out.reshape(num_head * dp, cdim)
+
+
+class PackedSelfAttention:
+    """AttentionPairBias weights with the head dimension padded to 32 or 64 (zero rows/columns)."""
+
+    def __init__(self, state: State, prefix: str, device, num_head: int = 16):
+        q = state[prefix + "q_projection.weight"].detach().float().cpu()
+        c = q.shape[0]
+        d = c // num_head
+        self.H, self.C, self.d = num_head, c, d
+        self.Dp = 32 if d <= 32 else 64
+        assert d <= 64
+        ws = [_pad_heads_rows(state[prefix + n + ".weight"].detach().float().cpu(), num_head, self.Dp)
+              for n in ("q_projection", "k_projection", "v_projection", "gating_query")]
+        self.w_qkvg = _b16(torch.cat(ws, 0), device)
+        wd = num_head * self.Dp
+        bias = torch.zeros(4 * wd)
+        qb = state.get(prefix + "q_projection.bias")
+        if qb is not None:
+            bias[:wd] = _pad_heads_rows(qb.detach().float().cpu()[:, None], num_head, self.Dp)[:, 0]
+        scale = torch.ones(4 * wd)
+        scale[:wd] = d ** -0.5
+        self.bias, self.scale = _f32(bias, device), _f32(scale, device)
+        t2 = state[prefix + "adaptive_zero_init.transition2.weight"].detach().float().cpu()  # [c_out, H*d]
+        self.w_out = _b16(_pad_heads_rows(t2.T.contiguous(), num_head, self.Dp).T.contiguous(), device)  # [c_out, H*Dp]
+
+
+class PackedPairformerBlock:
+    def __init__(self, state: State, prefix: str, device, with_single: bool = True):
+        self.tri_out = PackedTriMul(state, prefix + "triangle_multiplication_outgoing.", device)
+        self.tri_in = PackedTriMul(state, prefix + "triangle_multiplication_incoming.", device)
+        self.att_start = PackedTriAttn(state, prefix + "pair_attention1.", device)
+        self.att_end = PackedTriAttn(state, prefix + "pair_attention2.", device)
+        self.pair_transition = PackedTransition(state, prefix + "pair_transition.", device)
+        self.with_single = with_single
+        w = PairformerWeights()
+        w.tri_out, w.tri_in = self.tri_out.c, self.tri_in.c
+        w.att_start, w.att_end = self.att_start.c, self.att_end.c
+        w.pair_transition = self.pair_transition.c
+        if with_single:
+            self.spl_g = _f32(state.get(prefix + "single_pair_logits_norm.weight"), device)
+            self.spl_b = _f32(state.get(prefix + "single_pair_logits_norm.bias"), device)
+            self.spl_w = _f32(state[prefix + "single_pair_logits_projection.weight"], device)
+            self.sa = PackedSelfAttention(state, prefix + "single_attention_.", device, 16)
+            self.sa_ln_g = _f32(state.get(prefix + "single_attention_.adaptive_layernorm.layer_norm.weight"), device)
+            self.sa_ln_b = _f32(state.get(prefix + "single_attention_.adaptive_layernorm.layer_norm.bias"), device)
+            self.single_transition = PackedTransition(state, prefix + "single_transition.", device)
+            w.spl_ln_gamma, w.spl_ln_beta, w.spl_w = _ptr(self.spl_g), _ptr(self.spl_b), _ptr(self.spl_w)
+            w.sa_ln_gamma, w.sa_ln_beta = _ptr(self.sa_ln_g), _ptr(self.sa_ln_b)
+            w.sa_w_qkvg, w.sa_qkvg_bias, w.sa_qkvg_scale = _ptr(self.sa.w_qkvg), _ptr(self.sa.bias), _ptr(self.sa.scale)
+            w.sa_w_out = _ptr(self.sa.w_out)
+            w.single_transition = self.single_transition.c
+        self.c = w
+
+
+# ---------------------------------------------------------------------------------------------
+# operators
+# ---------------------------------------------------------------------------------------------
+def layernorm(x: torch.Tensor, gamma=None, beta=None, eps: float = 1e-5, proj_w: Optional[torch.Tensor] = None,
+              want_y: bool = True, mod_scale=None, mod_shift=None):
+    """LayerNorm over the last dim of a bf16 tensor (width 128 / 384 / 768).  With ``proj_w`` [H, C]
+    (float32) also returns proj [H, rows] float32.  ``mod_scale`` / ``mod_shift`` [rows_mod, C] bf16
+    apply the AdaLN modulation sigmoid(scale) * y + shift, broadcast over leading dims."""
+    _need_cuda(x, gamma, beta, proj_w)
+    assert x.dtype == BF16 and x.is_contiguous()
+    dev = _dev(x)
+    cdim = x.shape[-1]
+    rows = x.numel() // cdim
+    y = torch.empty_like(x) if want_y else None
+    h = 0 if proj_w is None else proj_w.shape[0]
+    proj = torch.empty(h, rows, dtype=torch.float32, device=x.device) if h else None
+    mod_rows = 0 if mod_scale is None else mod_scale.numel() // cdim
+    rc = load().xfold_layernorm_fwd(ctx(dev), _ptr(x), cdim, _ptr(y), cdim, rows, cdim, _ptr(gamma), _ptr(beta), eps, h,
+                                    _ptr(proj_w), _ptr(proj), rows, _ptr(mod_scale), _ptr(mod_shift), mod_rows,
+                                    _stream(dev))
+    check(rc, dev, "xfold_layernorm_fwd")
+    return (y, proj) if h else y
+
+
+def swiglu(x: torch.Tensor) -> torch.Tensor:
+    _need_cuda(x)
+    assert x.dtype == BF16 and x.is_contiguous()
+    dev = _dev(x)
+    f = x.shape[-1] // 2
+    out = torch.empty(*x.shape[:-1], f, dtype=BF16, device=x.device)
+    rc = load().xfold_swiglu_fwd(ctx(dev), _ptr(x), _ptr(out), x.numel() // (2 * f), f, _stream(dev))
+    check(rc, dev, "xfold_swiglu_fwd")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias=None, scale=None) -> torch.Tensor:
+    """x [..., K] bf16, w [N, K] bf16 -> [..., N] bf16 ((x w^T + bias) * scale)."""
+    _need_cuda(x, w, bias, scale)
+    assert x.dtype == BF16 and w.dtype == BF16 and x.is_contiguous() and w.is_contiguous()
+    dev = _dev(x)
+    k, n = x.shape[-1], w.shape[0]
+    m = x.numel() // k
+    out = torch.empty(*x.shape[:-1], n, dtype=BF16, device=x.device)
+    rc = load().xfold_linear_fwd(ctx(dev), _ptr(x), k, m, k, _ptr(w), n, _ptr(bias), _ptr(scale), _ptr(out), n, _stream(dev))
+    check(rc, dev, "xfold_linear_fwd")
+    return out
+
+
+def linear_gate_residual(x, w, gate=None, resid=None, row_gate_mod: int = 0, out=None):
+    _need_cuda(x, w, gate, resid)
+    dev = _dev(x)
+    k, n = x.shape[-1], w.shape[0]
+    m = x.numel() // k
+    if out is None:
+        out = torch.empty(*x.shape[:-1], n, dtype=BF16, device=x.device)
+    rc = load().xfold_linear_gate_residual_fwd(ctx(dev), _ptr(x), k, m, k, _ptr(w), n, _ptr(gate), n, row_gate_mod,
+                                               _ptr(resid), n, _ptr(out), n, _stream(dev))
+    check(rc, dev, "xfold_linear_gate_residual_fwd")
+    return out
+
+
+def linear_swiglu(x, w_packed):
+    _need_cuda(x, w_packed)
+    dev = _dev(x)
+    k, f = x.shape[-1], w_packed.shape[0] // 2
+    m = x.numel() // k
+    out = torch.empty(*x.shape[:-1], f, dtype=BF16, device=x.device)
+    rc = load().xfold_linear_swiglu_fwd(ctx(dev), _ptr(x), k, m, k, _ptr(w_packed), f, _ptr(out), f, _stream(dev))
+    check(rc, dev, "xfold_linear_swiglu_fwd")
+    return out
+
+
+def batched_contract(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """out[c, i, j] = sum_k a[c, i, k] * b[c, j, k]; the last dim must be a multiple of 8."""
+    _need_cuda(a, b)
+    assert a.dtype == BF16 and b.dtype == BF16 and a.is_contiguous() and b.is_contiguous()
+    dev = _dev(a)
+    ch, mi, kk = a.shape
+    nj = b.shape[1]
+    ldo = (nj + 7) // 8 * 8
+    out = torch.empty(ch, mi, ldo, dtype=BF16, device=a.device)
+    rc = load().xfold_batched_contract_fwd(ctx(dev), _ptr(a), _ptr(b), _ptr(out), ch, mi, nj, kk, kk, mi * kk, nj * kk,
+                                           ldo, mi * ldo, _stream(dev))
+    check(rc, dev, "xfold_batched_contract_fwd")
+    return out[:, :, :nj]
+
+
+def triangle_multiplication_(z: torch.Tensor, mask: Optional[torch.Tensor], w: PackedTriMul, outgoing: bool):
+    """In place: z += TriangleMultiplication(z, mask).  z bf16 [N, N, 128]; mask float32 [N, N]."""
+    _need_cuda(z, mask)
+    assert z.dtype == BF16 and z.is_contiguous() and z.shape[0] == z.shape[1] and z.shape[2] == 128
+    dev = _dev(z)
+    n = z.shape[0]
+    lib = load()
+    nb = lib.xfold_trimul_workspace_bytes(n)
+    ws = _Workspace.get(dev, nb)
+    if mask is not None:
+        mask = mask.to(torch.float32).contiguous()
+    rc = lib.xfold_triangle_multiplication_fwd(ctx(dev), _ptr(z), _ptr(mask), n, int(outgoing), C.byref(w.c), _ptr(ws),
+                                               ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_triangle_multiplication_fwd")
+    return z
+
+
+def triangle_attention_(z: torch.Tensor, mask: Optional[torch.Tensor], w: PackedTriAttn, transpose: bool):
+    """In place: z += TriangleAttention(z, mask) (starting node, or ending node when ``transpose``)."""
+    _need_cuda(z, mask)
+    assert z.dtype == BF16 and z.is_contiguous() and z.shape[0] == z.shape[1] and z.shape[2] == 128
+    dev = _dev(z)
+    n = z.shape[0]
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_triattn_workspace_bytes(n))
+    if mask is not None:
+        mask = mask.to(torch.float32).contiguous()
+    rc = lib.xfold_triangle_attention_fwd(ctx(dev), _ptr(z), _ptr(mask), n, int(transpose), C.byref(w.c), _ptr(ws),
+                                          ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_triangle_attention_fwd")
+    return z
+
+
+def transition_(x: torch.Tensor, w: PackedTransition):
+    """In place: x += Transition(x) over the last dim (128 or 384)."""
+    _need_cuda(x)
+    assert x.dtype == BF16 and x.is_contiguous() and x.shape[-1] == w.C
+    dev = _dev(x)
+    rows = x.numel() // w.C
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_transition_workspace_bytes(rows, w.C, w.F))
+    rc = lib.xfold_transition_fwd(ctx(dev), _ptr(x), rows, w.C, w.F, C.byref(w.c), _ptr(ws), ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_transition_fwd")
+    return x
+
+
+def attention_pair_bias_core(xn: torch.Tensor, w: PackedSelfAttention, pair_bias: torch.Tensor,
+                             mask: Optional[torch.Tensor]) -> torch.Tensor:
+    """xn bf16 [B, S, C] (normalised input), pair_bias float32 [H, S, S], mask float32 [S]
+    -> gated attention output bf16 [B, S, H * Dp] (head dim padded to Dp)."""
+    _need_cuda(xn, pair_bias, mask)
+    assert xn.dtype == BF16 and xn.is_contiguous() and pair_bias.dtype == torch.float32 and pair_bias.is_contiguous()
+    dev = _dev(xn)
+    b, s, cdim = xn.shape
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_apb_workspace_bytes(b, s, w.H, w.Dp))
+    out = torch.empty(b, s, w.H * w.Dp, dtype=BF16, device=xn.device)
+    if mask is not None:
+        mask = mask.to(torch.float32).contiguous()
+    rc = lib.xfold_attention_pair_bias_core_fwd(ctx(dev), _ptr(xn), b, s, cdim, w.H, w.Dp, _ptr(w.w_qkvg), _ptr(w.bias),
+                                                _ptr(w.scale), _ptr(pair_bias), _ptr(mask), _ptr(out), _ptr(ws),
+                                                ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_attention_pair_bias_core_fwd")
+    return out
+
+
+def pairformer_block_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq_mask, w: PackedPairformerBlock):
+    """In place: one Pairformer block on z bf16 [N, N, 128] and s bf16 [N, 384]."""
+    _need_cuda(z, s, pair_mask, seq_mask)
+    assert z.dtype == BF16 and z.is_contiguous()
+    dev = _dev(z)
+    n = z.shape[0]
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_pairformer_workspace_bytes(n))
+    pm = None if pair_mask is None else pair_mask.to(torch.float32).contiguous()
+    sm = None if seq_mask is None else seq_mask.to(torch.float32).contiguous()
+    rc = lib.xfold_pairformer_block_fwd(ctx(dev), _ptr(z), _ptr(s), _ptr(pm), _ptr(sm), n, C.byref(w.c), _ptr(ws),
+                                        ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_pairformer_block_fwd")
+    return z, s

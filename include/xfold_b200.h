@@ -1,0 +1,177 @@
+/* C ABI of libxfold_b200.so: the sm_100a replacement for the reference's fused CPU operator
+ * library (the `_alpha_attention` ops of src/distributed_xfold/xsmm_kernels/csrc/Alpha_Attention.cpp)
+ * and for the module forwards that sit directly on top of it.
+ *
+ * Conventions
+ *  - every function returns XFOLD_OK (0) or a non-zero status; xfold_last_error() gives the text;
+ *  - all tensor arguments are DEVICE pointers owned by the caller; activations and weights are
+ *    bf16 (passed as void*), masks / LayerNorm parameters / biases are float32;
+ *  - `stream` is a cudaStream_t passed as void*; calls are asynchronous on that stream;
+ *  - the library allocates nothing except the context (one status word on the device); scratch
+ *    memory is passed in by the caller (`ws`, size from the matching *_workspace_bytes function);
+ *  - kernels never wait unboundedly: a wait that runs out records a code in the context's status
+ *    word, the kernel drains and returns, and xfold_check_status() reports XFOLD_ERR_TIMEOUT.
+ */
+#ifndef XFOLD_B200_H_
+#define XFOLD_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  XFOLD_OK = 0,
+  XFOLD_ERR_ARG = 1,     /* bad argument (shape, alignment, null pointer, workspace too small) */
+  XFOLD_ERR_LAUNCH = 2,  /* CUDA reported an error at launch */
+  XFOLD_ERR_DEVICE = 3,  /* no usable device / driver entry point missing */
+  XFOLD_ERR_TIMEOUT = 4  /* an in-kernel bounded wait ran out (see xfold_check_status) */
+};
+
+typedef struct xfold_ctx xfold_ctx;
+
+/* Context: replaces the implicit process-wide state of the reference extension module
+ * (`tpp_pytorch_extension._C`, imported at prototypes/__init__.py:1). One per device. */
+int xfold_ctx_create(int device, xfold_ctx** out);
+void xfold_ctx_destroy(xfold_ctx* ctx);
+const char* xfold_last_error(xfold_ctx* ctx);
+/* Synchronises `stream`, reads and clears the device status word. */
+int xfold_check_status(xfold_ctx* ctx, void* stream);
+/* Version string with the build's gencode. */
+const char* xfold_version(void);
+
+/* ---- primitives -------------------------------------------------------------------------- */
+
+/* LayerNorm over rows of width C in {128, 384, 768}, eps as given (the reference uses 1e-5:
+ * LayerNormFwdTPP at csrc/triangle_multiplication.h:51-52, csrc/transition.h:26).
+ * gamma/beta may be NULL.  Optional fused projection: proj[h * proj_plane + row] =
+ * sum_c y[row][c] * proj_w[h][c] for num_proj in {0, 4, 16, 64} (the pair-bias projections of
+ * nn/d_attention.py:62 and nn/d_pairformer.py:158); y may then be NULL.  Optional AdaLN
+ * modulation (nn/d_diffusion_transformer.py:67-72): y = sigmoid(mod_scale[row % mod_rows]) * y
+ * + mod_shift[row % mod_rows], both bf16 [mod_rows][C], or NULL. */
+int xfold_layernorm_fwd(xfold_ctx* ctx, const void* x, long long ldx, void* y, long long ldy, long long rows, int C,
+                        const float* gamma, const float* beta, float eps, int num_proj, const float* proj_w,
+                        float* proj, long long proj_plane, const void* mod_scale, const void* mod_shift,
+                        int mod_rows, void* stream);
+
+/* SwiGLU: out[r][f] = silu(in[r][f]) * in[r][F + f]   (xfold.fastnn.gated_linear_unit as pinned by
+ * kernel_test/transition.py:37-43 and csrc/transition.h:65-88). */
+int xfold_swiglu_fwd(xfold_ctx* ctx, const void* in, void* out, long long rows, int F, void* stream);
+
+/* out[m][n] = (sum_k x[m][k] * w[n][k] + bias[n]) * scale[n]   (torch.nn.Linear; tcgen05 GEMM).
+ * K multiple of 8, ldx/ldo multiples of 8; bias / scale may be NULL. */
+int xfold_linear_fwd(xfold_ctx* ctx, const void* x, long long ldx, long long M, int K, const void* w, int N,
+                     const float* bias, const float* scale, void* out, long long ldo, void* stream);
+
+/* out[m][n] = resid[m][n] + (sum_k x[m][k] w[n][k]) * sigmoid(gate[m][n])   (gate and/or resid may be NULL;
+ * out may alias resid).  row_gate: gate shared by rows with the same (m % row_gate_mod). */
+int xfold_linear_gate_residual_fwd(xfold_ctx* ctx, const void* x, long long ldx, long long M, int K, const void* w,
+                                   int N, const void* gate, long long ldg, int row_gate_mod, const void* resid,
+                                   long long ldr, void* out, long long ldo, void* stream);
+
+/* h[m][f] = silu(x w_a[f]) * (x w_b[f]) with w packed in 256-row tiles [128 rows of w_a | 128 rows of w_b]. */
+int xfold_linear_swiglu_fwd(xfold_ctx* ctx, const void* x, long long ldx, long long M, int K, const void* w_packed,
+                            int F, void* out, long long ldo, void* stream);
+
+/* Batched contraction out[c][i][j] = sum_k a[c][i][k] * b[c][j][k] (the per-channel N x N x N product of
+ * TriangleMultiplication: 'cik,cjk->cij' at nn/d_triangle_multiplication.py:122-124). */
+int xfold_batched_contract_fwd(xfold_ctx* ctx, const void* a, const void* b, void* out, int channels, int Mi, int Nj,
+                               int Kk, long long ld, long long chan_stride_a, long long chan_stride_b,
+                               long long ldo, long long chan_stride_o, void* stream);
+
+/* ---- TriangleMultiplication ------------------------------------------------------------------
+ * Replaces `_alpha_attention::traingle_multiplication_forward` (csrc/Alpha_Attention.cpp:148-169,
+ * 206-210) together with the residual add of nn/d_pairformer.py:122-123: z += TriMul(z, mask).
+ * z: bf16 [N][N][128] updated in place; mask: float32 [N][N] or NULL. */
+typedef struct {
+  const float* ln_in_gamma;  /* left_norm_input  [128] */
+  const float* ln_in_beta;
+  const void* w_in;          /* bf16 [640][128]: rows 0..127 projection(a), 128..255 gate(a), 256..383 projection(b),
+                                384..511 gate(b), 512..639 gating_linear  (a = even rows, b = odd rows of the
+                                reference's interleaved weights, nn/d_triangle_multiplication.py:128-129) */
+  const float* ln_c_gamma;   /* center_norm [128] */
+  const float* ln_c_beta;
+  const void* w_out;         /* bf16 [128][128] output_projection */
+} xfold_trimul_weights;
+
+size_t xfold_trimul_workspace_bytes(int N);
+int xfold_triangle_multiplication_fwd(xfold_ctx* ctx, void* z, const float* mask, int N, int outgoing,
+                                      const xfold_trimul_weights* w, void* ws, size_t ws_bytes, void* stream);
+
+/* ---- TriangleAttention (GridSelfAttention) ---------------------------------------------------
+ * Replaces `_alpha_attention::grid_self_attn_forward` (csrc/Alpha_Attention.cpp:50-70, 182-185) plus the
+ * LayerNorm, pair-bias projection, optional transpose and residual add that the reference does in
+ * Python (nn/d_attention.py:58-88, nn/d_pairformer.py:132, 144): z += Attn(LN(z)).
+ * transpose = 0: starting node (attend along the second token axis); 1: ending node. */
+typedef struct {
+  const float* ln_gamma;   /* act_norm [128] */
+  const float* ln_beta;
+  const float* w_bias;     /* float32 [4][128] pair_bias_projection */
+  const void* w_qkvg;      /* bf16 [512][128]: q, k, v, gating_query rows (head-major inside each) */
+  const float* qkvg_scale; /* float32 [512]: D^-0.5 on the q columns, 1 elsewhere */
+  const void* w_out;       /* bf16 [128][128] output_projection */
+} xfold_triattn_weights;
+
+size_t xfold_triattn_workspace_bytes(int N);
+int xfold_triangle_attention_fwd(xfold_ctx* ctx, void* z, const float* mask, int N, int transpose,
+                                 const xfold_triattn_weights* w, void* ws, size_t ws_bytes, void* stream);
+
+/* ---- Transition ----------------------------------------------------------------------------------
+ * Replaces `_alpha_attention::transition_forward` (csrc/Alpha_Attention.cpp:116-125, 187-189) and
+ * DistributeTransition.forward (nn/d_primitives.py:31-38) plus the residual add: x += W2 swiglu(W1 LN(x)).
+ * C in {128, 384}; F = factor * C. */
+typedef struct {
+  const float* ln_gamma;
+  const float* ln_beta;
+  const void* w1_packed; /* bf16 [2F][C] in 256-row tiles [128 SiLU rows | 128 linear rows] */
+  const void* w2;        /* bf16 [C][F] */
+} xfold_transition_weights;
+
+size_t xfold_transition_workspace_bytes(long long rows, int C, int F);
+int xfold_transition_fwd(xfold_ctx* ctx, void* x, long long rows, int C, int F, const xfold_transition_weights* w,
+                         void* ws, size_t ws_bytes, void* stream);
+
+/* ---- AttentionPairBias core ------------------------------------------------------------------
+ * Replaces `_alpha_attention::batch_diffusion_self_attention_forward` (csrc/Alpha_Attention.cpp:72-92,
+ * 191-194): gated multi-head attention with query bias and an additive [H][S][S] pair bias, no
+ * output projection.  xn: bf16 [B][S][C] (already normalised); heads x head_dim = C; the head
+ * dimension is padded to Dp in {32, 64} inside the packed weights:
+ *   w_qkvg bf16 [4 * H * Dp][C], qkvg_bias / qkvg_scale float32 [4 * H * Dp];
+ * out: bf16 [B][S][H * Dp] (pad columns are zero).  mask: float32 [S] or NULL. */
+size_t xfold_apb_workspace_bytes(int B, int S, int H, int Dp);
+int xfold_attention_pair_bias_core_fwd(xfold_ctx* ctx, const void* xn, int B, int S, int C, int H, int Dp,
+                                       const void* w_qkvg, const float* qkvg_bias, const float* qkvg_scale,
+                                       const float* pair_bias, const float* mask, void* out, void* ws,
+                                       size_t ws_bytes, void* stream);
+
+/* ---- PairformerBlock --------------------------------------------------------------------------
+ * DistributePairformerBlock.forward (nn/d_pairformer.py:99-171) for world size 1: both TriMuls,
+ * both TriAttns, pair Transition, then pair-logit projection, single AttentionPairBias (16 heads x 24,
+ * padded to 32) and single Transition.  z [N][N][128] and s [N][384] are bf16, updated in place. */
+typedef struct {
+  xfold_trimul_weights tri_out, tri_in;
+  xfold_triattn_weights att_start, att_end;
+  xfold_transition_weights pair_transition;
+  /* single path (all NULL when the block has no single representation) */
+  const float* spl_ln_gamma;  /* single_pair_logits_norm [128] */
+  const float* spl_ln_beta;
+  const float* spl_w;         /* float32 [16][128] single_pair_logits_projection */
+  const float* sa_ln_gamma;   /* single_attention_.adaptive_layernorm.layer_norm [384] */
+  const float* sa_ln_beta;
+  const void* sa_w_qkvg;      /* bf16 [2048][384] */
+  const float* sa_qkvg_bias;  /* float32 [2048] */
+  const float* sa_qkvg_scale; /* float32 [2048] */
+  const void* sa_w_out;       /* bf16 [384][512] adaptive_zero_init.transition2 with padded head columns */
+  xfold_transition_weights single_transition;
+} xfold_pairformer_weights;
+
+size_t xfold_pairformer_workspace_bytes(int N);
+int xfold_pairformer_block_fwd(xfold_ctx* ctx, void* z, void* s, const float* pair_mask, const float* seq_mask,
+                               int N, const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* XFOLD_B200_H_ */
