@@ -47,6 +47,9 @@ SIGNATURES = {
     "xfold_last_error": (C.c_char_p, [vp]),
     "xfold_check_status": (ci, [vp, vp]),
     "xfold_version": (C.c_char_p, []),
+    "xfold_launch_count": (ll, [vp]),
+    "xfold_profile_enable": (ci, [vp, ci]),
+    "xfold_profile_read": (ci, [vp, ci, C.POINTER(cf), C.POINTER(ci)]),
     "xfold_layernorm_fwd": (ci, [vp, vp, ll, vp, ll, ll, ci, vp, vp, cf, ci, vp, vp, ll, vp, vp, ci, vp]),
     "xfold_swiglu_fwd": (ci, [vp, vp, vp, ll, ci, vp]),
     "xfold_linear_fwd": (ci, [vp, vp, ll, ll, ci, vp, ci, vp, vp, vp, ll, vp]),

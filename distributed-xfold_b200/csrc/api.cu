@@ -409,10 +409,38 @@ int xfold_ctx_create(int device, xfold_ctx** out) {
 void xfold_ctx_destroy(xfold_ctx* c) {
   if (!c) return;
   if (c->d_status) cudaFree(c->d_status);
+  for (auto& r : c->prof_recs) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  for (auto& r : c->prof_pool) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
   delete c;
 }
 
 const char* xfold_last_error(xfold_ctx* c) { return c ? c->last_error : "null context"; }
+
+long long xfold_launch_count(xfold_ctx* c) { return c ? c->launch_count : 0; }
+
+int xfold_profile_enable(xfold_ctx* c, int on) {
+  if (!c) return XFOLD_ERR_ARG;
+  c->prof_on = on;
+  return XFOLD_OK;
+}
+
+int xfold_profile_read(xfold_ctx* c, int kernel_class, float* ms_total, int* launches) {
+  if (!c || !ms_total || !launches) return XFOLD_ERR_ARG;
+  if (cudaDeviceSynchronize() != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "profile read: device error");
+  float total = 0.f;
+  int n = 0;
+  std::vector<ProfRec> keep;
+  for (auto& r : c->prof_recs) {
+    if (r.tag != kernel_class) { keep.push_back(r); continue; }
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) { total += ms; ++n; }
+    c->prof_pool.push_back(r);
+  }
+  c->prof_recs.swap(keep);
+  *ms_total = total;
+  *launches = n;
+  return XFOLD_OK;
+}
 
 int xfold_check_status(xfold_ctx* c, void* stream) {
   if (!c) return XFOLD_ERR_ARG;

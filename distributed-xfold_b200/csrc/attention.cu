@@ -363,6 +363,7 @@ int launch_maskb(Ctx* c, const float* mask, long long mask_ld, float* out, int B
   if (n <= 0) return XFOLD_OK;
   long long blocks = (n + 255) / 256;
   if (blocks > 4096) blocks = 4096;
+  ProfScope ps(c, XFOLD_K_MASK_BIAS, st);
   maskb_kernel<<<(int)blocks, 256, 0, st>>>(mask, mask_ld, out, B, S, ld);
   return check_launch(c, "maskb_kernel");
 }
@@ -373,6 +374,7 @@ int launch_attention(Ctx* c, int D, const CUtensorMap& tm, const AttnArgs& a, in
   if (qt <= 0 || a.B <= 0 || head_groups <= 0) return XFOLD_OK;
   if (a.B > 65535 || head_groups > 65535) return fail(c, XFOLD_ERR_ARG, "attention: batch %d / head groups %d exceed the grid limit", a.B, head_groups);
   dim3 grid(qt, head_groups, a.B);
+  ProfScope ps(c, XFOLD_K_ATTENTION, st);
   if (D == 32) {
     if (!attr_done[0][c->device & 7]) {
       cudaError_t e = cudaFuncSetAttribute(attn_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);

@@ -314,6 +314,11 @@ static int launch_one(Ctx* c, const CUtensorMap& tmA, const CUtensorMap& tmB, co
   const long long total = (long long)a.batches * a.tiles_m * a.tiles_n;
   if (total <= 0) return XFOLD_OK;
   const int grid = (int)(total < c->sm_count ? total : c->sm_count);
+  const int tag = EPI == EPI_TRIMUL_AB ? XFOLD_K_TRIMUL_PROJ
+                  : EPI == EPI_SWIGLU  ? XFOLD_K_LINEAR_SWIGLU
+                  : EPI == EPI_GATE_RESID ? XFOLD_K_LINEAR_GATE_RESID
+                  : (a.batches > 1 ? XFOLD_K_TRIMUL_CONTRACT : XFOLD_K_LINEAR);
+  ProfScope ps(c, tag, st);
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, a);
   return check_launch(c, "gemm_tn_kernel");
 }

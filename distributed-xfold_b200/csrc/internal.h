@@ -5,17 +5,53 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <vector>
+
 #include "../../include/xfold_b200.h"
 
 namespace xf {
 
 typedef __nv_bfloat16 bf16;
 
+struct ProfRec {
+  cudaEvent_t a, b;
+  int tag;
+};
+
 struct Ctx {
   int device = 0;
   int sm_count = 148;
   int* d_status = nullptr;  // one word: first in-kernel error code (0 = ok)
   char last_error[256] = {0};
+  long long launch_count = 0;  // kernels launched through this context
+  int prof_on = 0;             // when set, every launch is bracketed by a pair of CUDA events
+  std::vector<ProfRec> prof_recs, prof_pool;
+};
+
+// Brackets one kernel launch with events on its stream while profiling is enabled, and counts it.
+struct ProfScope {
+  Ctx* c;
+  cudaStream_t st;
+  ProfRec r;
+  bool on;
+  ProfScope(Ctx* c_, int tag, cudaStream_t st_) : c(c_), st(st_), on(c_->prof_on != 0) {
+    c->launch_count++;
+    if (!on) return;
+    if (!c->prof_pool.empty()) {
+      r = c->prof_pool.back();
+      c->prof_pool.pop_back();
+    } else {
+      cudaEventCreate(&r.a);
+      cudaEventCreate(&r.b);
+    }
+    r.tag = tag;
+    cudaEventRecord(r.a, st);
+  }
+  ~ProfScope() {
+    if (!on) return;
+    cudaEventRecord(r.b, st);
+    c->prof_recs.push_back(r);
+  }
 };
 
 // returns XFOLD_OK or sets ctx->last_error and returns a status code

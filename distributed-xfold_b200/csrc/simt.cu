@@ -110,6 +110,7 @@ static int launch_ln_c(Ctx* c, const bf16* x, long long ldx, bf16* y, long long 
   const long long cap = (long long)c->sm_count * 16;
   if (blocks > cap) blocks = cap;
   if (blocks <= 0) return XFOLD_OK;
+  ProfScope ps(c, XFOLD_K_LAYERNORM, st);
   switch (H) {
     case 0: ln_rows_kernel<C, 0><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows); break;
     case 4: ln_rows_kernel<C, 4><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows); break;
@@ -210,6 +211,7 @@ int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, int ld, int R, i
   long long blocks = ntiles;
   const long long cap = (long long)c->sm_count * 8;
   if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_CHANNEL_LN, st);
   cm_ln_kernel<<<(int)blocks, 256, 0, st>>>(in, chan_stride, ld, R, N, out, gamma, beta, eps);
   return check_launch(c, "cm_ln_kernel");
 }
@@ -244,6 +246,7 @@ int launch_swiglu(Ctx* c, const bf16* in, bf16* out, long long rows, int F, cuda
   long long blocks = (n8 + 255) / 256;
   const long long cap = (long long)c->sm_count * 16;
   if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_SWIGLU, st);
   swiglu_kernel<<<(int)blocks, 256, 0, st>>>(in, out, rows, F);
   return check_launch(c, "swiglu_kernel");
 }

@@ -42,6 +42,28 @@ int xfold_check_status(xfold_ctx* ctx, void* stream);
 /* Version string with the build's gencode. */
 const char* xfold_version(void);
 
+/* Kernel accounting (the counterpart of the reference's RECORD_SCOPE / SCOPEIT timers,
+ * csrc/Alpha_Attention.cpp:35-48).  xfold_launch_count: kernels launched through this context so
+ * far.  With profiling enabled every launch is bracketed by CUDA events on its stream;
+ * xfold_profile_read synchronises the device, returns the summed duration (ms) and the number of
+ * launches recorded for one kernel class since the last read of that class, and clears them. */
+enum {
+  XFOLD_K_LAYERNORM = 0,
+  XFOLD_K_TRIMUL_PROJ = 1,
+  XFOLD_K_TRIMUL_CONTRACT = 2,
+  XFOLD_K_CHANNEL_LN = 3,
+  XFOLD_K_LINEAR_GATE_RESID = 4,
+  XFOLD_K_LINEAR = 5,
+  XFOLD_K_ATTENTION = 6,
+  XFOLD_K_LINEAR_SWIGLU = 7,
+  XFOLD_K_MASK_BIAS = 8,
+  XFOLD_K_SWIGLU = 9,
+  XFOLD_K_COUNT = 10
+};
+long long xfold_launch_count(xfold_ctx* ctx);
+int xfold_profile_enable(xfold_ctx* ctx, int on);
+int xfold_profile_read(xfold_ctx* ctx, int kernel_class, float* ms_total, int* launches);
+
 /* ---- primitives -------------------------------------------------------------------------- */
 
 /* LayerNorm over rows of width C in {128, 384, 768}, eps as given (the reference uses 1e-5:

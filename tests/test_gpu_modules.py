@@ -66,8 +66,9 @@ def test_triangle_multiplication_golden(ops, oracle, golden, name):
     g = torch.Generator().manual_seed(meta["seed"])
     st = oracle.make_trimul_state(g, "")
     z = torch.randn(n, n, 128, generator=g)
-    mask = {"rand": lambda: torch.rand(n, n, generator=g), "ones": lambda: torch.ones(n, n),
-            "binary": lambda: (torch.rand(n, n, generator=g) > 0.2).float()}[meta["mask"]]()
+    # the generating script drew both random masks in turn, whichever it then used
+    r1, r2 = torch.rand(n, n, generator=g), torch.rand(n, n, generator=g)
+    mask = {"rand": r1, "ones": torch.ones(n, n), "binary": (r2 > 0.2).float()}[meta["mask"]]
     w = ops.PackedTriMul(st, "", "cuda")
     zd = z.to(BF).cuda().contiguous()
     ops.triangle_multiplication_(zd, mask.cuda(), w, meta["outgoing"])
