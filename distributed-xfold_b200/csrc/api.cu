@@ -11,9 +11,15 @@ namespace xf {
 struct AttnArgs;
 int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, int C, const float* g,
                    const float* b, float eps, int H, const float* pw, float* proj, long long plane, const bf16* msc,
-                   const bf16* msh, int mod_rows, cudaStream_t st);
-int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, int ld, int R, int N, bf16* out, const float* gamma,
-                 const float* beta, float eps, cudaStream_t st);
+                   const bf16* msh, int mod_rows, cudaStream_t st, bf16* proj_bf16 = nullptr, int trav_inner = 0,
+                   int trav_outer = 0, int proj_pitch = 0);
+int launch_mext(Ctx* c, const float* mask, long long mask_ld, bf16* out, int B, int S, cudaStream_t st);
+int launch_bias_transpose(Ctx* c, const float* in, bf16* out, int H, int S, int ldq, cudaStream_t st);
+int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0, int k_col0,
+                      int v_col0, int g_col0, int heads, const bf16* biasT, int ldq, const bf16* mext, int mext_rows,
+                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st);
+int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_stride, int R, int N, bf16* out,
+                 const float* gamma, const float* beta, float eps, cudaStream_t st);
 int launch_swiglu(Ctx* c, const bf16* in, bf16* out, long long rows, int F, cudaStream_t st);
 int launch_maskb(Ctx* c, const float* mask, long long mask_ld, float* out, int B, int S, int ld, cudaStream_t st);
 int launch_attention_op(Ctx* c, int D, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0,
@@ -246,19 +252,18 @@ static int trimul_fwd(Ctx* c, bf16* z, const float* mask, int N, int outgoing, c
 }
 
 struct TriAttnWs {
-  bf16 *x, *qkvg;
-  float *nb, *maskb;
-  int ldm;
+  bf16 *x, *qkvg, *nbT, *mext;
+  int ldq;
   size_t bytes;
 };
 static TriAttnWs carve_triattn(void* ws, size_t cap, int N) {
   TriAttnWs w;
   Carver cv(ws, cap);
-  w.ldm = (N + 127) / 128 * 128;
+  w.ldq = pad8(N);
   w.x = (bf16*)cv.take((size_t)N * N * 128 * 2);
   w.qkvg = (bf16*)cv.take((size_t)N * N * 512 * 2);
-  w.nb = (float*)cv.take((size_t)4 * N * N * 4);
-  w.maskb = (float*)cv.take((size_t)N * w.ldm * 4);
+  w.nbT = (bf16*)cv.take((size_t)4 * N * w.ldq * 2);
+  w.mext = (bf16*)cv.take((size_t)N * ((N + 127) / 128) * 4096);
   w.bytes = cv.off;
   return w;
 }
@@ -270,18 +275,20 @@ static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose,
   TriAttnWs W = carve_triattn(ws, ws_bytes, N);
   if (!ws || W.bytes > ws_bytes) return fail(c, XFOLD_ERR_ARG, "triattn: workspace too small (%zu < %zu)", ws_bytes, W.bytes);
   const long long M = (long long)N * N;
-  int rc = launch_ln_rows(c, z, 128, W.x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, W.nb, M, nullptr,
-                          nullptr, 0, st);
+  // x = LN(z) in token order; the pair bias is written key-major (bf16 [4][key][query]) by walking
+  // the tokens column by column, which is the layout the attention kernel's bias tensor map reads
+  int rc = launch_ln_rows(c, z, 128, W.x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, nullptr,
+                          (long long)N * W.ldq, nullptr, nullptr, 0, st, W.nbT, N, N, W.ldq);
   if (rc) return rc;
   rc = linear_plain(c, W.x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, W.qkvg, 512, st);
   if (rc) return rc;
-  rc = launch_maskb(c, mask, N, W.maskb, N, N, W.ldm, st);
+  rc = launch_mext(c, mask, N, W.mext, N, N, st);
   if (rc) return rc;
   // attention output (gated) goes to W.x, which is dead after the projection
   const long long seq_stride = transpose ? (long long)N * 128 : 128;
   const long long batch_stride = transpose ? 128 : (long long)N * 128;
-  rc = launch_attention_op(c, 32, W.qkvg, 512, N, N, transpose, 0, 128, 256, 384, 1, W.nb, M, N, W.maskb, W.ldm, W.x,
-                           seq_stride, batch_stride, st);
+  rc = launch_attention2(c, W.qkvg, 512, N, N, transpose, 0, 128, 256, 384, 4, W.nbT, W.ldq, W.mext, N, W.x, seq_stride,
+                         batch_stride, st);
   if (rc) return rc;
   return linear_gate_resid(c, W.x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, z, 128, z, 128, st);
 }
@@ -302,36 +309,52 @@ static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const x
   return linear_gate_resid(c, h, F, rows, F, (const bf16*)w->w2, C, nullptr, 0, 0, x, C, x, C, st);
 }
 
-static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, bf16** qkvg, float** maskb, int* ldm) {
+struct ApbWs {
+  bf16 *qkvg, *biasT, *mext;
+  float* maskb;
+  int ldm, ldq;
+};
+static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
   Carver local(nullptr, 0);
   if (!cv) cv = &local;
-  const int l = (S + 127) / 128 * 128;
-  bf16* q = (bf16*)cv->take((size_t)B * S * 4 * H * Dp * 2);
-  float* m = (float*)cv->take((size_t)l * 4);
-  if (qkvg) *qkvg = q;
-  if (maskb) *maskb = m;
-  if (ldm) *ldm = l;
+  ApbWs w;
+  w.ldm = (S + 127) / 128 * 128;
+  w.ldq = pad8(S);
+  w.qkvg = (bf16*)cv->take((size_t)B * S * 4 * H * Dp * 2);
+  w.maskb = (float*)cv->take((size_t)w.ldm * 4);
+  w.biasT = (bf16*)cv->take((size_t)H * S * w.ldq * 2);
+  w.mext = (bf16*)cv->take((size_t)(w.ldm / 128) * 4096);
+  if (out) *out = w;
   return cv->off;
 }
 
+// pair_bias: float32 [H][S][S] (query-major), or, when pair_biasT is given, bf16 [H][S][pad8(S)] key-major
 static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
-                        const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const float* mask,
-                        bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
-  if (!xn || !w_qkvg || !out || !pair_bias) return fail(c, XFOLD_ERR_ARG, "apb: null argument");
+                        const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
+                        const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (!xn || !w_qkvg || !out || (!pair_bias && !pair_biasT)) return fail(c, XFOLD_ERR_ARG, "apb: null argument");
   if ((Dp != 32 && Dp != 64) || (H * Dp) % 128) return fail(c, XFOLD_ERR_ARG, "apb: H x Dp must be a multiple of 128 with Dp 32 or 64");
   Carver cv(ws, ws_bytes);
-  bf16* qkvg;
-  float* maskb;
-  int ldm;
-  apb_ws(B, S, H, Dp, &cv, &qkvg, &maskb, &ldm);
+  ApbWs W;
+  apb_ws(B, S, H, Dp, &cv, &W);
   if (!ws || !cv.ok()) return fail(c, XFOLD_ERR_ARG, "apb: workspace too small (%zu < %zu)", ws_bytes, cv.off);
   const int Wd = H * Dp;
-  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, qkvg, 4 * Wd, st);
+  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, W.qkvg, 4 * Wd, st);
   if (rc) return rc;
-  rc = launch_maskb(c, mask, 0, maskb, 1, S, ldm, st);
+  if (Dp == 32) {
+    if (!pair_biasT) {
+      if ((rc = launch_bias_transpose(c, pair_bias, W.biasT, H, S, W.ldq, st))) return rc;
+      pair_biasT = W.biasT;
+    }
+    if ((rc = launch_mext(c, mask, 0, W.mext, 1, S, st))) return rc;
+    return launch_attention2(c, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, H, pair_biasT, W.ldq, W.mext, 1, out, Wd,
+                             (long long)S * Wd, st);
+  }
+  if (!pair_bias) return fail(c, XFOLD_ERR_ARG, "apb: the 64-wide head kernel takes the float32 query-major bias");
+  rc = launch_maskb(c, mask, 0, W.maskb, 1, S, W.ldm, st);
   if (rc) return rc;
-  return launch_attention_op(c, Dp, qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, Wd / 128, pair_bias, (long long)S * S, S,
-                             maskb, 0, out, Wd, (long long)S * Wd, st);
+  return launch_attention_op(c, Dp, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, Wd / 128, pair_bias, (long long)S * S, S,
+                             W.maskb, 0, out, Wd, (long long)S * Wd, st);
 }
 
 static size_t pairformer_ws_bytes(int N) {
@@ -340,8 +363,8 @@ static size_t pairformer_ws_bytes(int N) {
   size_t t = align_up((size_t)N * N * 128 * 2, 1024) + align_up((size_t)N * N * 512 * 2, 1024) + 2048;
   size_t m = a > b ? a : b;
   if (t > m) m = t;
-  // single path: pair logits [16][N][N] fp32 + xn [N][384] + attention scratch + o [N][512] + transition scratch
-  size_t s = align_up((size_t)16 * N * N * 4, 1024) + align_up((size_t)N * 384 * 2, 1024) + apb_ws(1, N, 16, 32, nullptr, nullptr, nullptr, nullptr) +
+  // single path: pair logits [16][N][pad8(N)] bf16 (sized as fp32 here) + xn [N][384] + attention scratch + o [N][512] + transition scratch
+  size_t s = align_up((size_t)16 * N * N * 4, 1024) + align_up((size_t)N * 384 * 2, 1024) + apb_ws(1, N, 16, 32, nullptr, nullptr) +
              align_up((size_t)N * 512 * 2, 1024) + align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 8192;
   return (m > s ? m : s) + 4096;
 }
@@ -358,21 +381,22 @@ static int pairformer_fwd(Ctx* c, bf16* z, bf16* s, const float* pair_mask, cons
   if ((rc = transition_fwd(c, z, (long long)N * N, 128, 512, &w->pair_transition, ws, ws_bytes, st))) return rc;
   if (!s || !w->spl_w) return XFOLD_OK;
   Carver cv(ws, ws_bytes);
-  float* pl = (float*)cv.take((size_t)16 * N * N * 4);
+  const int ldq = pad8(N);
+  bf16* pl = (bf16*)cv.take((size_t)16 * N * ldq * 2);
   bf16* xn = (bf16*)cv.take((size_t)N * 384 * 2);
   bf16* o = (bf16*)cv.take((size_t)N * 512 * 2);
-  const size_t apb_bytes = apb_ws(1, N, 16, 32, nullptr, nullptr, nullptr, nullptr);
+  const size_t apb_bytes = apb_ws(1, N, 16, 32, nullptr, nullptr);
   void* apb_scratch = cv.take(apb_bytes);
   const size_t tr_bytes = align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 2048;
   void* tr_scratch = cv.take(tr_bytes);
   if (!cv.ok()) return fail(c, XFOLD_ERR_ARG, "pairformer: workspace too small for the single path");
   const long long M = (long long)N * N;
-  if ((rc = launch_ln_rows(c, z, 128, nullptr, 128, M, 128, w->spl_ln_gamma, w->spl_ln_beta, 1e-5f, 16, w->spl_w, pl, M,
-                           nullptr, nullptr, 0, st))) return rc;
+  if ((rc = launch_ln_rows(c, z, 128, nullptr, 128, M, 128, w->spl_ln_gamma, w->spl_ln_beta, 1e-5f, 16, w->spl_w, nullptr,
+                           (long long)N * ldq, nullptr, nullptr, 0, st, pl, N, N, ldq))) return rc;
   if ((rc = launch_ln_rows(c, s, 384, xn, 384, N, 384, w->sa_ln_gamma, w->sa_ln_beta, 1e-5f, 0, nullptr, nullptr, 0,
                            nullptr, nullptr, 0, st))) return rc;
-  if ((rc = apb_core_fwd(c, xn, 1, N, 384, 16, 32, (const bf16*)w->sa_w_qkvg, w->sa_qkvg_bias, w->sa_qkvg_scale, pl,
-                         seq_mask, o, apb_scratch, apb_bytes, st))) return rc;
+  if ((rc = apb_core_fwd(c, xn, 1, N, 384, 16, 32, (const bf16*)w->sa_w_qkvg, w->sa_qkvg_bias, w->sa_qkvg_scale, nullptr,
+                         pl, seq_mask, o, apb_scratch, apb_bytes, st))) return rc;
   if ((rc = linear_gate_resid(c, o, 512, N, 512, (const bf16*)w->sa_w_out, 384, nullptr, 0, 0, s, 384, s, 384, st))) return rc;
   return transition_fwd(c, s, N, 384, 1536, &w->single_transition, tr_scratch, tr_bytes, st);
 }
@@ -525,14 +549,14 @@ int xfold_transition_fwd(xfold_ctx* c, void* x, long long rows, int C, int F, co
   return transition_fwd(c, (bf16*)x, rows, C, F, w, ws, ws_bytes, (cudaStream_t)stream);
 }
 
-size_t xfold_apb_workspace_bytes(int B, int S, int H, int Dp) { return apb_ws(B, S, H, Dp, nullptr, nullptr, nullptr, nullptr) + 2048; }
+size_t xfold_apb_workspace_bytes(int B, int S, int H, int Dp) { return apb_ws(B, S, H, Dp, nullptr, nullptr) + 2048; }
 int xfold_attention_pair_bias_core_fwd(xfold_ctx* c, const void* xn, int B, int S, int C, int H, int Dp,
                                        const void* w_qkvg, const float* qkvg_bias, const float* qkvg_scale,
                                        const float* pair_bias, const float* mask, void* out, void* ws, size_t ws_bytes,
                                        void* stream) {
   if (!c) return XFOLD_ERR_ARG;
-  return apb_core_fwd(c, (const bf16*)xn, B, S, C, H, Dp, (const bf16*)w_qkvg, qkvg_bias, qkvg_scale, pair_bias, mask,
-                      (bf16*)out, ws, ws_bytes, (cudaStream_t)stream);
+  return apb_core_fwd(c, (const bf16*)xn, B, S, C, H, Dp, (const bf16*)w_qkvg, qkvg_bias, qkvg_scale, pair_bias, nullptr,
+                      mask, (bf16*)out, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 size_t xfold_pairformer_workspace_bytes(int N) { return pairformer_ws_bytes(N); }

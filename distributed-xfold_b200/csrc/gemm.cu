@@ -2,8 +2,9 @@
 //
 //   warp 0      : TMA producer (one elected lane), 128-byte-swizzled K-major tiles, STAGES-deep ring
 //   warp 1      : tcgen05.mma issuer (one elected lane); owns the TMEM allocation (2 accumulators)
-//   warps 2..5  : epilogue; each warp owns one 32-lane quarter of the 128-row accumulator and
-//                 drains it with tcgen05.ld while the MMA warp already fills the other buffer
+//   warps 2..9  : epilogue; two warps share each 32-lane quarter of the 128-row accumulator (one per
+//                 half of the columns) and drain it with tcgen05.ld while the MMA warp already fills
+//                 the other buffer
 //
 // Every projection of the Pairformer block, the SwiGLU transition and the per-channel N x N x N
 // TriangleMultiplication contraction (batched over the 128 channels) run through this kernel; they
@@ -15,7 +16,7 @@ namespace xf {
 
 constexpr int BM = 128;
 constexpr int BK = 64;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
 template <int BN>
 struct GemmCfg {
@@ -75,7 +76,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull[s], 1);
-      mbar_init(&tempty[s], 4);
+      mbar_init(&tempty[s], 8);
     }
     *cta_abort = 0;
     fence_barrier_init();
@@ -142,7 +143,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const int q = warp & 3;          // TMEM lane quarter this warp may read
+    const int ch = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     const int row = q * 32 + lane;
     uint32_t it = 0;
     for (long long t = blockIdx.x; t < total; t += gridDim.x, ++it) {
@@ -160,7 +162,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         bf16* orow = p.out + (long long)b * p.out_batch_stride + m * p.ldo;
         const bool vec_ok = ((p.ldo & 7) == 0);
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 32; ++cc) {
+        for (int cc = ch * (BN / 64); cc < (ch + 1) * (BN / 64); ++cc) {
           uint32_t r[32];
           tmem_ld32(taddr + cc * 32, r);
           tmem_ld_wait();
@@ -212,7 +214,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const bool rvalid = m < p.M;
         bf16* orow = p.out + m * p.ldo + tn * (BN / 2);
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 64; ++cc) {
+        for (int cc = ch * (BN / 128); cc < (ch + 1) * (BN / 128); ++cc) {
           uint32_t ra[32], rb[32];
           tmem_ld32(taddr + cc * 32, ra);
           tmem_ld32(taddr + BN / 2 + cc * 32, rb);
@@ -249,7 +251,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const float mk = (rvalid && p.mask) ? p.mask[tok] : 1.f;
           bf16* dst = (tn == 0 ? p.out_a : p.out_b) + cm_off;
 #pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = ch * 2; cc < ch * 2 + 2; ++cc) {
             uint32_t rp[32], rg[32];
             tmem_ld32(taddr + cc * 32, rp);
             tmem_ld32(taddr + 128 + cc * 32, rg);
@@ -265,7 +267,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         } else {
           bf16* orow = p.out_g + tok * 128;
 #pragma unroll 1
-          for (int cc = 0; cc < 4; ++cc) {
+          for (int cc = ch * 2; cc < ch * 2 + 2; ++cc) {
             uint32_t r[32];
             tmem_ld32(taddr + cc * 32, r);
             tmem_ld_wait();

@@ -23,80 +23,130 @@ __global__ void __launch_bounds__(256)
 ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, long long ldy, long long rows,
                const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
                const float* __restrict__ pw, float* __restrict__ proj, long long proj_plane,
-               const bf16* __restrict__ mod_scale, const bf16* __restrict__ mod_shift, int mod_rows) {
+               const bf16* __restrict__ mod_scale, const bf16* __restrict__ mod_shift, int mod_rows,
+               bf16* __restrict__ proj_bf16, int trav_inner, int trav_outer, int proj_pitch) {
   constexpr int V = C / 128;  // uint2 (4 x bf16) vectors per lane
+  // rows a warp keeps in flight at once: the loads of all of them are issued before any is reduced
+  constexpr int RPW = (H == 0) ? (C == 128 ? 4 : 2) : (H == 4 ? 2 : 1);
   const int lane = threadIdx.x & 31;
   const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long row = warp_global; row < rows; row += nwarps) {
-    const uint2* xr = reinterpret_cast<const uint2*>(x + row * ldx);
-    float v[V][4];
-    float s = 0.f;
+  for (long long base = warp_global; base < rows; base += nwarps * RPW) {
+    uint2 raw[RPW][V];
+    long long srow[RPW], pidx[RPW];
+    bool valid[RPW];
 #pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const uint2 u = xr[lane + 32 * k];
-      v[k][0] = bf16_lo(u.x); v[k][1] = bf16_hi(u.x); v[k][2] = bf16_lo(u.y); v[k][3] = bf16_hi(u.y);
-      s += v[k][0] + v[k][1] + v[k][2] + v[k][3];
-    }
-    const float mean = warp_sum(s) * (1.f / C);
-    float ss = 0.f;
+    for (int j = 0; j < RPW; ++j) {
+      const long long prow = base + (long long)j * nwarps;
+      valid[j] = prow < rows;
+      // transposed traversal: projection index (y, x) = (prow / inner, prow % inner) reads source row x * outer + y
+      srow[j] = trav_inner > 0 ? (prow % trav_inner) * trav_outer + prow / trav_inner : prow;
+      pidx[j] = trav_inner > 0 ? (prow / trav_inner) * proj_pitch + prow % trav_inner : prow;
+      if (valid[j]) {
+        const uint2* xr = reinterpret_cast<const uint2*>(x + srow[j] * ldx);
 #pragma unroll
-    for (int k = 0; k < V; ++k)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[k][e] -= mean;
-        ss += v[k][e] * v[k][e];
-      }
-    const float rstd = rsqrtf(warp_sum(ss) * (1.f / C) + eps);
-#pragma unroll
-    for (int k = 0; k < V; ++k) {
-      const int c0 = (lane + 32 * k) * 4;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float t = v[k][e] * rstd;
-        if (gamma) t *= gamma[c0 + e];
-        if (beta) t += beta[c0 + e];
-        v[k][e] = t;
+        for (int k = 0; k < V; ++k) raw[j][k] = xr[lane + 32 * k];
       }
     }
-    if (mod_scale) {
-      const long long mr = row % mod_rows;
-      const uint2* sc = reinterpret_cast<const uint2*>(mod_scale + mr * C);
-      const uint2* sh = reinterpret_cast<const uint2*>(mod_shift + mr * C);
+#pragma unroll
+    for (int j = 0; j < RPW; ++j) {
+      if (!valid[j]) continue;
+      const long long row = srow[j];
+      float v[V][4];
+      float s = 0.f;
 #pragma unroll
       for (int k = 0; k < V; ++k) {
-        const uint2 a = sc[lane + 32 * k], b = sh[lane + 32 * k];
-        v[k][0] = sigmoidf_fast(bf16_lo(a.x)) * v[k][0] + bf16_lo(b.x);
-        v[k][1] = sigmoidf_fast(bf16_hi(a.x)) * v[k][1] + bf16_hi(b.x);
-        v[k][2] = sigmoidf_fast(bf16_lo(a.y)) * v[k][2] + bf16_lo(b.y);
-        v[k][3] = sigmoidf_fast(bf16_hi(a.y)) * v[k][3] + bf16_hi(b.y);
+        const uint2 u = raw[j][k];
+        v[k][0] = bf16_lo(u.x); v[k][1] = bf16_hi(u.x); v[k][2] = bf16_lo(u.y); v[k][3] = bf16_hi(u.y);
+        s += v[k][0] + v[k][1] + v[k][2] + v[k][3];
       }
-    }
-    if (y) {
-      uint2* yr = reinterpret_cast<uint2*>(y + row * ldy);
+      const float mean = warp_sum(s) * (1.f / C);
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[k][e] -= mean;
+          ss += v[k][e] * v[k][e];
+        }
+      const float rstd = rsqrtf(warp_sum(ss) * (1.f / C) + eps);
 #pragma unroll
       for (int k = 0; k < V; ++k) {
-        uint2 u;
-        u.x = pack_bf16x2(v[k][0], v[k][1]);
-        u.y = pack_bf16x2(v[k][2], v[k][3]);
-        yr[lane + 32 * k] = u;
-      }
-    }
-    if constexpr (H > 0) {
-      float acc[H];
+        const int c0 = (lane + 32 * k) * 4;
 #pragma unroll
-      for (int h = 0; h < H; ++h) {
-        float a = 0.f;
+        for (int e = 0; e < 4; ++e) {
+          float t = v[k][e] * rstd;
+          if (gamma) t *= gamma[c0 + e];
+          if (beta) t += beta[c0 + e];
+          v[k][e] = t;
+        }
+      }
+      if (mod_scale) {
+        const long long mr = row % mod_rows;
+        const uint2* sc = reinterpret_cast<const uint2*>(mod_scale + mr * C);
+        const uint2* sh = reinterpret_cast<const uint2*>(mod_shift + mr * C);
 #pragma unroll
         for (int k = 0; k < V; ++k) {
-          const float4 w = *reinterpret_cast<const float4*>(pw + h * C + (lane + 32 * k) * 4);
-          a += v[k][0] * w.x + v[k][1] * w.y + v[k][2] * w.z + v[k][3] * w.w;
+          const uint2 a = sc[lane + 32 * k], b = sh[lane + 32 * k];
+          v[k][0] = sigmoidf_fast(bf16_lo(a.x)) * v[k][0] + bf16_lo(b.x);
+          v[k][1] = sigmoidf_fast(bf16_hi(a.x)) * v[k][1] + bf16_hi(b.x);
+          v[k][2] = sigmoidf_fast(bf16_lo(a.y)) * v[k][2] + bf16_lo(b.y);
+          v[k][3] = sigmoidf_fast(bf16_hi(a.y)) * v[k][3] + bf16_hi(b.y);
         }
-        acc[h] = warp_sum(a);
       }
+      if (y) {
+        uint2* yr = reinterpret_cast<uint2*>(y + row * ldy);
 #pragma unroll
-      for (int h = 0; h < H; ++h)
-        if (lane == h) proj[(long long)h * proj_plane + row] = acc[h];
+        for (int k = 0; k < V; ++k) {
+          uint2 u;
+          u.x = pack_bf16x2(v[k][0], v[k][1]);
+          u.y = pack_bf16x2(v[k][2], v[k][3]);
+          yr[lane + 32 * k] = u;
+        }
+      }
+      if constexpr (H > 0) {
+        float acc[H];
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          float a = 0.f;
+#pragma unroll
+          for (int k = 0; k < V; ++k) {
+            const float4 w = *reinterpret_cast<const float4*>(pw + h * C + (lane + 32 * k) * 4);
+            a += v[k][0] * w.x + v[k][1] * w.y + v[k][2] * w.z + v[k][3] * w.w;
+          }
+          acc[h] = a;
+        }
+        if constexpr (H == 16) {
+          // recursive halving over lane bits 4..1: a lane ends with the sum of head (lane >> 1) & 15 over the
+          // 16 lanes that share its bit 0; one more exchange over bit 0 completes it
+#pragma unroll
+          for (int step = 0; step < 4; ++step) {
+            const int off = 16 >> step, n = 8 >> step;
+            const bool upper = (lane & off) != 0;
+#pragma unroll
+            for (int i = 0; i < n; ++i) {
+              const float send = upper ? acc[i] : acc[i + n];
+              const float keep = upper ? acc[i + n] : acc[i];
+              acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+          }
+          const float tot = acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 1);
+          const int h = (lane >> 1) & 15;
+          if ((lane & 1) == 0) {
+            if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(tot);
+            else proj[(long long)h * proj_plane + pidx[j]] = tot;
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < H; ++h) acc[h] = warp_sum(acc[h]);
+#pragma unroll
+          for (int h = 0; h < H; ++h)
+            if (lane == h) {
+              if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(acc[h]);
+              else proj[(long long)h * proj_plane + pidx[j]] = acc[h];
+            }
+        }
+      }
     }
   }
 }
@@ -104,7 +154,7 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
 template <int C>
 static int launch_ln_c(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, const float* g,
                        const float* b, float eps, int H, const float* pw, float* proj, long long plane,
-                       const bf16* msc, const bf16* msh, int mod_rows, cudaStream_t st) {
+                       const bf16* msc, const bf16* msh, int mod_rows, bf16* pbf, int tin, int tout, int tpitch, cudaStream_t st) {
   const int wpb = 8;
   long long blocks = (rows + wpb - 1) / wpb;
   const long long cap = (long long)c->sm_count * 16;
@@ -112,10 +162,10 @@ static int launch_ln_c(Ctx* c, const bf16* x, long long ldx, bf16* y, long long 
   if (blocks <= 0) return XFOLD_OK;
   ProfScope ps(c, XFOLD_K_LAYERNORM, st);
   switch (H) {
-    case 0: ln_rows_kernel<C, 0><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows); break;
-    case 4: ln_rows_kernel<C, 4><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows); break;
-    case 16: ln_rows_kernel<C, 16><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows); break;
-    case 64: ln_rows_kernel<C, 64><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows); break;
+    case 0: ln_rows_kernel<C, 0><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    case 4: ln_rows_kernel<C, 4><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    case 16: ln_rows_kernel<C, 16><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    case 64: ln_rows_kernel<C, 64><<<(int)blocks, 256, 0, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
     default: return fail(c, XFOLD_ERR_ARG, "layernorm: fused projection supports 0, 4, 16 or 64 outputs, got %d", H);
   }
   return check_launch(c, "ln_rows_kernel");
@@ -123,12 +173,12 @@ static int launch_ln_c(Ctx* c, const bf16* x, long long ldx, bf16* y, long long 
 
 int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, int C, const float* g,
                    const float* b, float eps, int H, const float* pw, float* proj, long long plane, const bf16* msc,
-                   const bf16* msh, int mod_rows, cudaStream_t st) {
+                   const bf16* msh, int mod_rows, cudaStream_t st, bf16* pbf, int tin, int tout, int tpitch) {
   if ((ldx & 3) || (ldy & 3)) return fail(c, XFOLD_ERR_ARG, "layernorm: row strides must be multiples of 4 elements");
   switch (C) {
-    case 128: return launch_ln_c<128>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, st);
-    case 384: return launch_ln_c<384>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, st);
-    case 768: return launch_ln_c<768>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, st);
+    case 128: return launch_ln_c<128>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
+    case 384: return launch_ln_c<384>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
+    case 768: return launch_ln_c<768>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
   }
   return fail(c, XFOLD_ERR_ARG, "layernorm: unsupported width %d (128, 384, 768)", C);
 }
@@ -138,50 +188,64 @@ int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy,
 // A block stages 128 channels x 64 tokens in shared memory (rows padded to 66 elements so that
 // the per-token reads below are bank-conflict free), 4 threads share a token.
 // ---------------------------------------------------------------------------------------------
-constexpr int CMLN_TOK = 64;
+constexpr int CMLN_TOK = 128;
+constexpr int CMLN_PITCH = CMLN_TOK + 8;  // elements; keeps every row 16-byte aligned
 __global__ void __launch_bounds__(256)
-cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, int ld, int R, int N, bf16* __restrict__ out,
-             const float* __restrict__ gamma, const float* __restrict__ beta, float eps) {
-  __shared__ bf16 tile[128][CMLN_TOK + 2];
+cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, long long row_stride, int R, int N,
+             bf16* __restrict__ out, const float* __restrict__ gamma, const float* __restrict__ beta, float eps) {
+  __shared__ __align__(16) bf16 tile[128][CMLN_PITCH];
+  __shared__ float psum[4][CMLN_TOK], psq[4][CMLN_TOK];
   const int tiles_j = (N + CMLN_TOK - 1) / CMLN_TOK;
   const long long ntiles = (long long)R * tiles_j;
+  const bool vec_ok = ((chan_stride | row_stride) & 7) == 0;
   for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
     const int i = int(t / tiles_j);
     const int j0 = int(t % tiles_j) * CMLN_TOK;
     __syncthreads();
-    // 128 rows of 64 tokens; a warp reads one channel row as 32 x 4-byte words
-    for (int idx = threadIdx.x; idx < 128 * 32; idx += 256) {
-      const int ch = idx >> 5, w = idx & 31;
-      const int j = j0 + 2 * w;
-      uint32_t u = 0;
-      const bf16* src = in + ch * chan_stride + (long long)i * ld + j;
-      if (j + 1 < N) u = *reinterpret_cast<const uint32_t*>(src);
-      else if (j < N) u = uint32_t(*reinterpret_cast<const uint16_t*>(src));
-      *reinterpret_cast<uint32_t*>(&tile[ch][2 * w]) = u;
+    // 128 channel rows x 128 tokens: 16 x 16-byte loads per row
+    for (int idx = threadIdx.x; idx < 128 * 16; idx += 256) {
+      const int ch = idx >> 4, w = idx & 15;
+      const int j = j0 + 8 * w;
+      const bf16* src = in + ch * chan_stride + (long long)i * row_stride + j;
+      uint4 u = make_uint4(0, 0, 0, 0);
+      if (vec_ok && j + 7 < N) u = *reinterpret_cast<const uint4*>(src);
+      else {
+        bf16 tmp[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) tmp[e] = (j + e < N) ? src[e] : __float2bfloat16(0.f);
+        u = *reinterpret_cast<uint4*>(tmp);
+      }
+      *reinterpret_cast<uint4*>(&tile[ch][8 * w]) = u;
     }
     __syncthreads();
-    const int tk = threadIdx.x >> 2, part = threadIdx.x & 3;  // token in tile, quarter of the channels
-    float v[32];
-    float s = 0.f;
+    // thread = (token pair tp, quarter of the channels): a warp reads 32 consecutive 4-byte words per channel row
+    const int tp = threadIdx.x & 63, part = threadIdx.x >> 6;
+    float v0[32], v1[32];
+    float s0 = 0.f, s1 = 0.f, q0 = 0.f, q1 = 0.f;
 #pragma unroll
     for (int e = 0; e < 32; ++e) {
-      v[e] = __bfloat162float(tile[part * 32 + e][tk]);
-      s += v[e];
+      const uint32_t u = *reinterpret_cast<const uint32_t*>(&tile[part * 32 + e][2 * tp]);
+      v0[e] = bf16_lo(u);
+      v1[e] = bf16_hi(u);
+      s0 += v0[e]; s1 += v1[e];
+      q0 += v0[e] * v0[e]; q1 += v1[e] * v1[e];
     }
-    s += __shfl_xor_sync(0xffffffffu, s, 1);
-    s += __shfl_xor_sync(0xffffffffu, s, 2);
-    const float mean = s * (1.f / 128);
-    float ss = 0.f;
+    psum[part][2 * tp] = s0; psum[part][2 * tp + 1] = s1;
+    psq[part][2 * tp] = q0; psq[part][2 * tp + 1] = q1;
+    __syncthreads();
+    float mean[2], rstd[2];
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      v[e] -= mean;
-      ss += v[e] * v[e];
+    for (int u = 0; u < 2; ++u) {
+      const int tk = 2 * tp + u;
+      const float sm = psum[0][tk] + psum[1][tk] + psum[2][tk] + psum[3][tk];
+      const float sq = psq[0][tk] + psq[1][tk] + psq[2][tk] + psq[3][tk];
+      mean[u] = sm * (1.f / 128);
+      rstd[u] = rsqrtf(fmaxf(sq * (1.f / 128) - mean[u] * mean[u], 0.f) + eps);
     }
-    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
-    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
-    const float rstd = rsqrtf(ss * (1.f / 128) + eps);
-    const int j = j0 + tk;
-    if (j < N) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int j = j0 + 2 * tp + u;
+      if (j >= N) continue;
       bf16* orow = out + ((long long)i * N + j) * 128 + part * 32;
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) {
@@ -189,30 +253,29 @@ cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, int ld, int R, 
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           const int ch = part * 32 + g8 * 8 + e;
-          float tv = v[g8 * 8 + e] * rstd;
+          float tv = ((u ? v1[g8 * 8 + e] : v0[g8 * 8 + e]) - mean[u]) * rstd[u];
           if (gamma) tv *= gamma[ch];
           if (beta) tv += beta[ch];
           o[e] = tv;
         }
-        uint4 u;
-        u.x = pack_bf16x2(o[0], o[1]); u.y = pack_bf16x2(o[2], o[3]);
-        u.z = pack_bf16x2(o[4], o[5]); u.w = pack_bf16x2(o[6], o[7]);
-        *reinterpret_cast<uint4*>(orow + g8 * 8) = u;
+        uint4 w4;
+        w4.x = pack_bf16x2(o[0], o[1]); w4.y = pack_bf16x2(o[2], o[3]);
+        w4.z = pack_bf16x2(o[4], o[5]); w4.w = pack_bf16x2(o[6], o[7]);
+        *reinterpret_cast<uint4*>(orow + g8 * 8) = w4;
       }
     }
   }
 }
 
-int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, int ld, int R, int N, bf16* out, const float* gamma,
-                 const float* beta, float eps, cudaStream_t st) {
-  if (ld & 1) return fail(c, XFOLD_ERR_ARG, "cm_ln: leading dimension must be even");
+int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_stride, int R, int N, bf16* out,
+                 const float* gamma, const float* beta, float eps, cudaStream_t st) {
   const long long ntiles = (long long)R * ((N + CMLN_TOK - 1) / CMLN_TOK);
   if (ntiles <= 0) return XFOLD_OK;
   long long blocks = ntiles;
   const long long cap = (long long)c->sm_count * 8;
   if (blocks > cap) blocks = cap;
   ProfScope ps(c, XFOLD_K_CHANNEL_LN, st);
-  cm_ln_kernel<<<(int)blocks, 256, 0, st>>>(in, chan_stride, ld, R, N, out, gamma, beta, eps);
+  cm_ln_kernel<<<(int)blocks, 256, 0, st>>>(in, chan_stride, row_stride, R, N, out, gamma, beta, eps);
   return check_launch(c, "cm_ln_kernel");
 }
 

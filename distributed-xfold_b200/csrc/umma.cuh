@@ -112,6 +112,13 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       : "memory");
 }
 
+// plain (untiled) bulk copy global -> shared; addresses and size are multiples of 16 bytes
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
 // ------------------------------------------------------------------------------------
 // tcgen05: TMEM allocation, MMA, commit, loads
 // ------------------------------------------------------------------------------------
@@ -168,6 +175,17 @@ __device__ __forceinline__ uint64_t make_sdesc(uint32_t saddr, uint32_t lbo_byte
   return d;
 }
 
+// Un-swizzled K-major tile made of 8-row x 16-byte core matrices (128 B each, rows 16 B apart):
+// lbo = byte distance between core matrices along K, sbo = between 8-row groups along M/N.
+__device__ __forceinline__ uint64_t make_sdesc_noswizzle(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((saddr & 0x3FFFFu) >> 4);
+  d |= uint64_t((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= uint64_t((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= uint64_t(1) << 46;
+  return d;
+}
+
 // 32 lanes x 32 columns of fp32: thread l of the warp receives row (lane base + l), columns c .. c+31.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -186,7 +204,12 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // ------------------------------------------------------------------------------------
 // misc math
 // ------------------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5: one MUFU op (tanh.approx, rel. error ~2^-11) instead of ex2 + rcp
+__device__ __forceinline__ float sigmoidf_fast(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return fmaf(0.5f, t, 0.5f);
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
