@@ -64,6 +64,15 @@ SIGNATURES = {
     "xfold_transition_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp, sz, vp]),
     "xfold_apb_workspace_bytes": (sz, [ci, ci, ci, ci]),
     "xfold_attention_pair_bias_core_fwd": (ci, [vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
+    "xfold_trimul_project_fwd": (ci, [vp, vp, vp, ci, ci, C.POINTER(TriMulWeights), vp, vp, vp, vp, ci, vp]),
+    "xfold_trimul_contract_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, vp, ci, vp]),
+    "xfold_trimul_output_fwd": (ci, [vp, vp, ci, vp, ci, ci, C.POINTER(TriMulWeights), vp, vp, vp]),
+    "xfold_triattn_bias_fwd": (ci, [vp, vp, ci, ci, C.POINTER(TriAttnWeights), vp, vp, ci, ll, ci, vp]),
+    "xfold_triattn_core_scratch_bytes": (sz, [ci, ci, C.POINTER(sz)]),
+    "xfold_triattn_core_fwd": (ci, [vp, vp, vp, ci, vp, ll, ci, ci, C.POINTER(TriAttnWeights), vp, vp, vp, vp]),
+    "xfold_pair_logits_fwd": (ci, [vp, vp, ci, ci, vp, vp, vp, vp, ci, ll, ci, vp]),
+    "xfold_single_update_workspace_bytes": (sz, [ci]),
+    "xfold_single_update_fwd": (ci, [vp, vp, vp, ci, vp, ci, C.POINTER(PairformerWeights), vp, sz, vp]),
     "xfold_pairformer_workspace_bytes": (sz, [ci]),
     "xfold_pairformer_block_fwd": (ci, [vp, vp, vp, vp, vp, ci, C.POINTER(PairformerWeights), vp, sz, vp]),
 }

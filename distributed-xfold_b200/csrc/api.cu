@@ -179,6 +179,77 @@ static int batched_contract(Ctx* c, const bf16* a_, const bf16* b_, bf16* out, i
 // ---------------------------------------------------------------------------------------------
 static inline int pad8(int n) { return (n + 7) & ~7; }
 
+// a / b are stored "row-interleaved channel-major": element (row i, channel c, k) at (i * 128 + c) * ld + k.
+// A rank's rows are one contiguous block, so the all-gather of b over the row-shard group is a plain
+// concatenation, and the per-channel operand of the contraction is a strided 2-D slice for TMA.
+static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N, int transposed_store,
+                          const xfold_trimul_weights* w, bf16* x, bf16* a_out, bf16* b_out, bf16* g, int ld,
+                          cudaStream_t st) {
+  const long long M = (long long)R * N;
+  int rc = launch_ln_rows(c, z, 128, x, 128, M, 128, w->ln_in_gamma, w->ln_in_beta, 1e-5f, 0, nullptr, nullptr, 0,
+                          nullptr, nullptr, 0, st);
+  if (rc) return rc;
+  CUtensorMap tA, tB;
+  bool ok;
+  GemmArgs a;
+  if (!transposed_store) {
+    ok = make_tmap_bf16_3d(&tA, x, 128, M, 1, 128, (uint64_t)128 * M, 64, 128, 1);
+    a.a_row_mode = 0;
+    a.tiles_m = (int)((M + 127) / 128);
+  } else {  // tile rows step along the first token axis, second axis fixed: a[j][c][i] (needs R == N)
+    ok = make_tmap_bf16_3d(&tA, x, 128, N, R, 128, (uint64_t)128 * N, 64, 1, 128);
+    a.a_row_mode = 1;
+    a.a_dim1 = N;
+    a.tiles_m = N * ((R + 127) / 128);
+  }
+  ok = ok && make_tmap_bf16_3d(&tB, w->w_in, 128, 640, 1, 128, 128 * 640, 64, 256, 1);
+  if (!ok) return fail(c, XFOLD_ERR_ARG, "trimul: cannot encode projection tensor maps");
+  a.M = (int)M;
+  a.N = 640;
+  a.K = 128;
+  a.tiles_n = 3;
+  a.out_a = a_out;
+  a.out_b = b_out;
+  a.out_g = g;
+  a.cm_chan_stride = ld;
+  a.cm_ld = 128 * ld;
+  a.ntok = N;
+  a.mask = mask;
+  a.status = c->d_status;
+  return launch_gemm(c, EPI_TRIMUL_AB, 256, tA, tB, a, st);
+}
+
+// o[i][c][j] = sum_k a[i][c][k] * b[j][c][k]   (a: Ri rows, b: Nj rows, both [.][128][ld]; o: [Ri][128][ldo])
+static int trimul_contract(Ctx* c, const bf16* a_, const bf16* b_, int Ri, int Nj, int K, int ld, bf16* o, int ldo,
+                           cudaStream_t st) {
+  if ((ld & 7) || (ldo & 7)) return fail(c, XFOLD_ERR_ARG, "contract: leading dimensions must be multiples of 8");
+  CUtensorMap tA, tB;
+  if (!make_tmap_bf16_3d(&tA, a_, K, Ri, 128, (uint64_t)128 * ld, ld, 64, 128, 1) ||
+      !make_tmap_bf16_3d(&tB, b_, K, Nj, 128, (uint64_t)128 * ld, ld, 64, 256, 1))
+    return fail(c, XFOLD_ERR_ARG, "contract: cannot encode tensor maps");
+  GemmArgs a;
+  a.M = Ri;
+  a.N = Nj;
+  a.K = K;
+  a.batches = 128;
+  a.b_batched = 1;
+  a.tiles_m = (Ri + 127) / 128;
+  a.tiles_n = (Nj + 255) / 256;
+  a.out = o;
+  a.ldo = (long long)128 * ldo;
+  a.out_batch_stride = ldo;
+  a.status = c->d_status;
+  return launch_gemm(c, EPI_PLAIN, 256, tA, tB, a, st);
+}
+
+// z (+)= Linear(LN_c(o)) * sigmoid(g); o: [R][128][ldo]; x: scratch [R*N][128]
+static int trimul_output(Ctx* c, const bf16* o, int ldo, const bf16* g, int R, int N, const xfold_trimul_weights* w,
+                         bf16* x, bf16* z, cudaStream_t st) {
+  int rc = launch_cm_ln(c, o, ldo, (long long)128 * ldo, R, N, x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
+  if (rc) return rc;
+  return linear_gate_resid(c, x, 128, (long long)R * N, 128, (const bf16*)w->w_out, 128, g, 128, 0, z, 128, z, 128, st);
+}
+
 struct TriMulWs {
   bf16 *x, *a, *b, *g, *o;
   int ld;
@@ -205,50 +276,12 @@ static int trimul_fwd(Ctx* c, bf16* z, const float* mask, int N, int outgoing, c
   if (N <= 0) return XFOLD_OK;
   TriMulWs W = carve_trimul(ws, ws_bytes, N);
   if (!ws || W.bytes > ws_bytes) return fail(c, XFOLD_ERR_ARG, "trimul: workspace too small (%zu < %zu)", ws_bytes, W.bytes);
-  const long long M = (long long)N * N;
-  int rc = launch_ln_rows(c, z, 128, W.x, 128, M, 128, w->ln_in_gamma, w->ln_in_beta, 1e-5f, 0, nullptr, nullptr, 0,
-                          nullptr, nullptr, 0, st);
+  // incoming: a and b are stored transposed, so that o[i][c][j] = sum_k bT[i][c][k] aT[j][c][k] is the same product
+  int rc = trimul_project(c, z, mask, N, N, outgoing ? 0 : 1, w, W.x, W.a, W.b, W.g, W.ld, st);
   if (rc) return rc;
-  // gated projections -> a, b channel-major (incoming: stored transposed), gating_linear -> g token-major
-  {
-    CUtensorMap tA, tB;
-    bool ok;
-    GemmArgs a;
-    if (outgoing) {
-      ok = make_tmap_bf16_3d(&tA, W.x, 128, M, 1, 128, (uint64_t)128 * M, 64, 128, 1);
-      a.a_row_mode = 0;
-      a.tiles_m = (int)((M + 127) / 128);
-    } else {
-      ok = make_tmap_bf16_3d(&tA, W.x, 128, N, N, 128, (uint64_t)128 * N, 64, 1, 128);
-      a.a_row_mode = 1;
-      a.a_dim1 = N;
-      a.tiles_m = N * ((N + 127) / 128);
-    }
-    ok = ok && make_tmap_bf16_3d(&tB, w->w_in, 128, 640, 1, 128, 128 * 640, 64, 256, 1);
-    if (!ok) return fail(c, XFOLD_ERR_ARG, "trimul: cannot encode projection tensor maps");
-    a.M = (int)M;
-    a.N = 640;
-    a.K = 128;
-    a.tiles_n = 3;
-    a.out_a = W.a;
-    a.out_b = W.b;
-    a.out_g = W.g;
-    a.cm_chan_stride = (long long)N * W.ld;
-    a.cm_ld = W.ld;
-    a.ntok = N;
-    a.mask = mask;
-    a.status = c->d_status;
-    rc = launch_gemm(c, EPI_TRIMUL_AB, 256, tA, tB, a, st);
-    if (rc) return rc;
-  }
-  // contraction: outgoing o[c][i][j] = sum_k a[c][i][k] b[c][j][k]; incoming uses the transposed stores:
-  // o[c][i][j] = sum_k bT[c][i][k] aT[c][j][k]
-  const long long cs = (long long)N * W.ld;
-  rc = batched_contract(c, outgoing ? W.a : W.b, outgoing ? W.b : W.a, W.o, 128, N, N, N, W.ld, cs, cs, W.ld, cs, st);
+  rc = trimul_contract(c, outgoing ? W.a : W.b, outgoing ? W.b : W.a, N, N, N, W.ld, W.o, W.ld, st);
   if (rc) return rc;
-  rc = launch_cm_ln(c, W.o, cs, W.ld, N, N, W.x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
-  if (rc) return rc;
-  return linear_gate_resid(c, W.x, 128, M, 128, (const bf16*)w->w_out, 128, W.g, 128, 0, z, 128, z, 128, st);
+  return trimul_output(c, W.o, W.ld, W.g, N, N, w, W.x, z, st);
 }
 
 struct TriAttnWs {
@@ -256,41 +289,59 @@ struct TriAttnWs {
   int ldq;
   size_t bytes;
 };
-static TriAttnWs carve_triattn(void* ws, size_t cap, int N) {
+static TriAttnWs carve_triattn(void* ws, size_t cap, int R, int N) {
   TriAttnWs w;
   Carver cv(ws, cap);
   w.ldq = pad8(N);
-  w.x = (bf16*)cv.take((size_t)N * N * 128 * 2);
-  w.qkvg = (bf16*)cv.take((size_t)N * N * 512 * 2);
+  w.x = (bf16*)cv.take((size_t)R * N * 128 * 2);
+  w.qkvg = (bf16*)cv.take((size_t)R * N * 512 * 2);
   w.nbT = (bf16*)cv.take((size_t)4 * N * w.ldq * 2);
-  w.mext = (bf16*)cv.take((size_t)N * ((N + 127) / 128) * 4096);
+  w.mext = (bf16*)cv.take((size_t)R * ((N + 127) / 128) * 4096);
   w.bytes = cv.off;
   return w;
+}
+
+// x = LN(z) for a block of R rows, plus the pair bias those rows contribute, written bf16:
+//   key_major_rows == 0: rows are QUERY rows x: biasT[h][y][x_local] (walks the tokens column by column)
+//   key_major_rows == 1: rows are KEY rows:      biasT[h][row_local][y]  (row-major walk)
+// pitch is the row pitch of the destination (elements), plane its per-head stride.
+static int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weights* w, bf16* x, bf16* biasT,
+                        int pitch, long long plane, int key_major_rows, cudaStream_t st) {
+  const long long M = (long long)R * N;
+  if (!key_major_rows)
+    return launch_ln_rows(c, z, 128, x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, nullptr, plane, nullptr,
+                          nullptr, 0, st, biasT, R, N, pitch);
+  // linear walk with a padded pitch: "inner" = N tokens per row, source row = prow itself
+  return launch_ln_rows(c, z, 128, x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, nullptr, plane, nullptr,
+                        nullptr, 0, st, biasT, -N, 0, pitch);
+}
+
+// z (+)= out_proj(gated attention(x)) for R batch rows (sequence length N); biasT: bf16 [4][N][ldq] key-major.
+// transposed: the R x N token grid is stored [N][R] (sequence index outermost), used by the single-GPU ending node.
+static int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
+                        int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st) {
+  const long long M = (long long)R * N;
+  int rc = linear_plain(c, x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, qkvg, 512, st);
+  if (rc) return rc;
+  if ((rc = launch_mext(c, mask, mask_ld, mext, R, N, st))) return rc;
+  const long long seq_stride = transposed ? (long long)R * 128 : 128;
+  const long long batch_stride = transposed ? 128 : (long long)N * 128;
+  rc = launch_attention2(c, qkvg, 512, N, R, transposed, 0, 128, 256, 384, 4, biasT, ldq, mext, R, x, seq_stride,
+                         batch_stride, st);
+  if (rc) return rc;
+  return linear_gate_resid(c, x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, z, 128, z, 128, st);
 }
 
 static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose, const xfold_triattn_weights* w, void* ws,
                        size_t ws_bytes, cudaStream_t st) {
   if (!z || !w || !w->w_qkvg || !w->w_out || !w->w_bias) return fail(c, XFOLD_ERR_ARG, "triattn: null argument");
   if (N <= 0) return XFOLD_OK;
-  TriAttnWs W = carve_triattn(ws, ws_bytes, N);
+  TriAttnWs W = carve_triattn(ws, ws_bytes, N, N);
   if (!ws || W.bytes > ws_bytes) return fail(c, XFOLD_ERR_ARG, "triattn: workspace too small (%zu < %zu)", ws_bytes, W.bytes);
-  const long long M = (long long)N * N;
-  // x = LN(z) in token order; the pair bias is written key-major (bf16 [4][key][query]) by walking
-  // the tokens column by column, which is the layout the attention kernel's bias tensor map reads
-  int rc = launch_ln_rows(c, z, 128, W.x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, nullptr,
-                          (long long)N * W.ldq, nullptr, nullptr, 0, st, W.nbT, N, N, W.ldq);
+  // both nodes use bias(q, k) = projection of token (q, k), not transposed for the ending node
+  int rc = triattn_bias(c, z, N, N, w, W.x, W.nbT, W.ldq, (long long)N * W.ldq, 0, st);
   if (rc) return rc;
-  rc = linear_plain(c, W.x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, W.qkvg, 512, st);
-  if (rc) return rc;
-  rc = launch_mext(c, mask, N, W.mext, N, N, st);
-  if (rc) return rc;
-  // attention output (gated) goes to W.x, which is dead after the projection
-  const long long seq_stride = transpose ? (long long)N * 128 : 128;
-  const long long batch_stride = transpose ? 128 : (long long)N * 128;
-  rc = launch_attention2(c, W.qkvg, 512, N, N, transpose, 0, 128, 256, 384, 4, W.nbT, W.ldq, W.mext, N, W.x, seq_stride,
-                         batch_stride, st);
-  if (rc) return rc;
-  return linear_gate_resid(c, W.x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, z, 128, z, 128, st);
+  return triattn_core(c, W.x, W.nbT, W.ldq, mask, N, N, N, transpose, w, W.qkvg, W.mext, z, st);
 }
 
 static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
@@ -357,15 +408,39 @@ static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int 
                              W.maskb, 0, out, Wd, (long long)S * Wd, st);
 }
 
+static size_t single_ws_bytes(int N) {
+  return align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 512 * 2, 1024) + apb_ws(1, N, 16, 32, nullptr, nullptr) +
+         align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 16384;
+}
+
+// single += AttentionPairBias(single, pair logits) ; single += Transition(single)   (nn/d_pairformer.py:162-169)
+// plT: bf16 [16][N][ldq] key-major pair logits.
+static int single_update(Ctx* c, bf16* s, const bf16* plT, int ldq, const float* seq_mask, int N,
+                         const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, cudaStream_t st) {
+  Carver cv(ws, ws_bytes);
+  bf16* xn = (bf16*)cv.take((size_t)N * 384 * 2);
+  bf16* o = (bf16*)cv.take((size_t)N * 512 * 2);
+  const size_t apb_bytes = apb_ws(1, N, 16, 32, nullptr, nullptr);
+  void* apb_scratch = cv.take(apb_bytes);
+  const size_t tr_bytes = align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 2048;
+  void* tr_scratch = cv.take(tr_bytes);
+  if (!ws || !cv.ok()) return fail(c, XFOLD_ERR_ARG, "single update: workspace too small (%zu < %zu)", ws_bytes, cv.off);
+  int rc;
+  if ((rc = launch_ln_rows(c, s, 384, xn, 384, N, 384, w->sa_ln_gamma, w->sa_ln_beta, 1e-5f, 0, nullptr, nullptr, 0,
+                           nullptr, nullptr, 0, st))) return rc;
+  if ((rc = apb_core_fwd(c, xn, 1, N, 384, 16, 32, (const bf16*)w->sa_w_qkvg, w->sa_qkvg_bias, w->sa_qkvg_scale, nullptr,
+                         plT, seq_mask, o, apb_scratch, apb_bytes, st))) return rc;
+  if ((rc = linear_gate_resid(c, o, 512, N, 512, (const bf16*)w->sa_w_out, 384, nullptr, 0, 0, s, 384, s, 384, st))) return rc;
+  return transition_fwd(c, s, N, 384, 1536, &w->single_transition, tr_scratch, tr_bytes, st);
+}
+
 static size_t pairformer_ws_bytes(int N) {
   size_t a = carve_trimul(nullptr, 0, N).bytes;
-  size_t b = carve_triattn(nullptr, 0, N).bytes;
+  size_t b = carve_triattn(nullptr, 0, N, N).bytes;
   size_t t = align_up((size_t)N * N * 128 * 2, 1024) + align_up((size_t)N * N * 512 * 2, 1024) + 2048;
   size_t m = a > b ? a : b;
   if (t > m) m = t;
-  // single path: pair logits [16][N][pad8(N)] bf16 (sized as fp32 here) + xn [N][384] + attention scratch + o [N][512] + transition scratch
-  size_t s = align_up((size_t)16 * N * N * 4, 1024) + align_up((size_t)N * 384 * 2, 1024) + apb_ws(1, N, 16, 32, nullptr, nullptr) +
-             align_up((size_t)N * 512 * 2, 1024) + align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 8192;
+  size_t s = align_up((size_t)16 * N * pad8(N) * 2, 1024) + single_ws_bytes(N) + 4096;
   return (m > s ? m : s) + 4096;
 }
 
@@ -383,22 +458,12 @@ static int pairformer_fwd(Ctx* c, bf16* z, bf16* s, const float* pair_mask, cons
   Carver cv(ws, ws_bytes);
   const int ldq = pad8(N);
   bf16* pl = (bf16*)cv.take((size_t)16 * N * ldq * 2);
-  bf16* xn = (bf16*)cv.take((size_t)N * 384 * 2);
-  bf16* o = (bf16*)cv.take((size_t)N * 512 * 2);
-  const size_t apb_bytes = apb_ws(1, N, 16, 32, nullptr, nullptr);
-  void* apb_scratch = cv.take(apb_bytes);
-  const size_t tr_bytes = align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 2048;
-  void* tr_scratch = cv.take(tr_bytes);
+  void* rest = cv.take(single_ws_bytes(N));
   if (!cv.ok()) return fail(c, XFOLD_ERR_ARG, "pairformer: workspace too small for the single path");
   const long long M = (long long)N * N;
   if ((rc = launch_ln_rows(c, z, 128, nullptr, 128, M, 128, w->spl_ln_gamma, w->spl_ln_beta, 1e-5f, 16, w->spl_w, nullptr,
                            (long long)N * ldq, nullptr, nullptr, 0, st, pl, N, N, ldq))) return rc;
-  if ((rc = launch_ln_rows(c, s, 384, xn, 384, N, 384, w->sa_ln_gamma, w->sa_ln_beta, 1e-5f, 0, nullptr, nullptr, 0,
-                           nullptr, nullptr, 0, st))) return rc;
-  if ((rc = apb_core_fwd(c, xn, 1, N, 384, 16, 32, (const bf16*)w->sa_w_qkvg, w->sa_qkvg_bias, w->sa_qkvg_scale, nullptr,
-                         pl, seq_mask, o, apb_scratch, apb_bytes, st))) return rc;
-  if ((rc = linear_gate_resid(c, o, 512, N, 512, (const bf16*)w->sa_w_out, 384, nullptr, 0, 0, s, 384, s, 384, st))) return rc;
-  return transition_fwd(c, s, N, 384, 1536, &w->single_transition, tr_scratch, tr_bytes, st);
+  return single_update(c, s, pl, ldq, seq_mask, N, w, rest, single_ws_bytes(N), st);
 }
 
 }  // namespace xf
@@ -533,7 +598,7 @@ int xfold_triangle_multiplication_fwd(xfold_ctx* c, void* z, const float* mask, 
   return trimul_fwd(c, (bf16*)z, mask, N, outgoing, w, ws, ws_bytes, (cudaStream_t)stream);
 }
 
-size_t xfold_triattn_workspace_bytes(int N) { return carve_triattn(nullptr, 0, N).bytes; }
+size_t xfold_triattn_workspace_bytes(int N) { return carve_triattn(nullptr, 0, N, N).bytes; }
 int xfold_triangle_attention_fwd(xfold_ctx* c, void* z, const float* mask, int N, int transpose,
                                  const xfold_triattn_weights* w, void* ws, size_t ws_bytes, void* stream) {
   if (!c) return XFOLD_ERR_ARG;
@@ -564,6 +629,54 @@ int xfold_pairformer_block_fwd(xfold_ctx* c, void* z, void* s, const float* pair
                                const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream) {
   if (!c) return XFOLD_ERR_ARG;
   return pairformer_fwd(c, (bf16*)z, (bf16*)s, pair_mask, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+/* ---- row-shard stages ------------------------------------------------------------------------ */
+int xfold_trimul_project_fwd(xfold_ctx* c, const void* z, const float* mask, int R, int N, const xfold_trimul_weights* w,
+                             void* x_scratch, void* a, void* b, void* g, int ld, void* stream) {
+  if (!c || !z || !w || !x_scratch || !a || !b || !g) return XFOLD_ERR_ARG;
+  if (ld < N || (ld & 7)) return fail(c, XFOLD_ERR_ARG, "trimul project: ld must be >= N and a multiple of 8");
+  return trimul_project(c, (const bf16*)z, mask, R, N, 0, w, (bf16*)x_scratch, (bf16*)a, (bf16*)b, (bf16*)g, ld, (cudaStream_t)stream);
+}
+int xfold_trimul_contract_fwd(xfold_ctx* c, const void* a, const void* b_full, int R, int Nj, int K, int ld, void* o, int ldo,
+                              void* stream) {
+  if (!c || !a || !b_full || !o) return XFOLD_ERR_ARG;
+  return trimul_contract(c, (const bf16*)a, (const bf16*)b_full, R, Nj, K, ld, (bf16*)o, ldo, (cudaStream_t)stream);
+}
+int xfold_trimul_output_fwd(xfold_ctx* c, const void* o, int ldo, const void* g, int R, int N, const xfold_trimul_weights* w,
+                            void* x_scratch, void* z, void* stream) {
+  if (!c || !o || !g || !w || !x_scratch || !z) return XFOLD_ERR_ARG;
+  return trimul_output(c, (const bf16*)o, ldo, (const bf16*)g, R, N, w, (bf16*)x_scratch, (bf16*)z, (cudaStream_t)stream);
+}
+int xfold_triattn_bias_fwd(xfold_ctx* c, const void* z, int R, int N, const xfold_triattn_weights* w, void* x, void* biasT,
+                           int pitch, long long plane, int key_major_rows, void* stream) {
+  if (!c || !z || !w || !x || !biasT) return XFOLD_ERR_ARG;
+  return triattn_bias(c, (const bf16*)z, R, N, w, (bf16*)x, (bf16*)biasT, pitch, plane, key_major_rows, (cudaStream_t)stream);
+}
+size_t xfold_triattn_core_scratch_bytes(int R, int N, size_t* mext_bytes) {
+  if (mext_bytes) *mext_bytes = (size_t)R * ((N + 127) / 128) * 4096;
+  return (size_t)R * N * 512 * 2;
+}
+int xfold_triattn_core_fwd(xfold_ctx* c, void* x, const void* biasT, int ldq, const float* mask, long long mask_ld, int R,
+                           int N, const xfold_triattn_weights* w, void* qkvg_scratch, void* mext_scratch, void* z,
+                           void* stream) {
+  if (!c || !x || !biasT || !w || !qkvg_scratch || !mext_scratch || !z) return XFOLD_ERR_ARG;
+  return triattn_core(c, (bf16*)x, (const bf16*)biasT, ldq, mask, mask_ld, R, N, 0, w, (bf16*)qkvg_scratch,
+                      (bf16*)mext_scratch, (bf16*)z, (cudaStream_t)stream);
+}
+int xfold_pair_logits_fwd(xfold_ctx* c, const void* z, int R, int N, const float* ln_gamma, const float* ln_beta,
+                          const float* w16, void* plT, int pitch, long long plane, int key_major_rows, void* stream) {
+  if (!c || !z || !w16 || !plT) return XFOLD_ERR_ARG;
+  const long long M = (long long)R * N;
+  return launch_ln_rows(c, (const bf16*)z, 128, nullptr, 128, M, 128, ln_gamma, ln_beta, 1e-5f, 16, w16, nullptr, plane,
+                        nullptr, nullptr, 0, (cudaStream_t)stream, (bf16*)plT, key_major_rows ? -N : R, key_major_rows ? 0 : N,
+                        pitch);
+}
+size_t xfold_single_update_workspace_bytes(int N) { return single_ws_bytes(N); }
+int xfold_single_update_fwd(xfold_ctx* c, void* s, const void* plT, int ldq, const float* seq_mask, int N,
+                            const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream) {
+  if (!c || !s || !plT || !w) return XFOLD_ERR_ARG;
+  return single_update(c, (bf16*)s, (const bf16*)plT, ldq, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -40,8 +40,10 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
       const long long prow = base + (long long)j * nwarps;
       valid[j] = prow < rows;
       // transposed traversal: projection index (y, x) = (prow / inner, prow % inner) reads source row x * outer + y
-      srow[j] = trav_inner > 0 ? (prow % trav_inner) * trav_outer + prow / trav_inner : prow;
-      pidx[j] = trav_inner > 0 ? (prow / trav_inner) * proj_pitch + prow % trav_inner : prow;
+      // trav_inner < 0: plain walk, but the projection rows (of -trav_inner entries) have pitch proj_pitch
+      const long long inner = trav_inner > 0 ? trav_inner : -trav_inner;
+      srow[j] = trav_inner > 0 ? (prow % inner) * trav_outer + prow / inner : prow;
+      pidx[j] = trav_inner != 0 ? (prow / inner) * proj_pitch + prow % inner : prow;
       if (valid[j]) {
         const uint2* xr = reinterpret_cast<const uint2*>(x + srow[j] * ldx);
 #pragma unroll

@@ -352,3 +352,122 @@ def pairformer_block_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq
                                         ws.numel(), _stream(dev))
     check(rc, dev, "xfold_pairformer_block_fwd")
     return z, s
+
+
+# ---------------------------------------------------------------------------------------------
+# row-shard stages (the multi-GPU block composes these with collectives in between)
+# ---------------------------------------------------------------------------------------------
+def _pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def stage_trimul_project(z: torch.Tensor, mask_shard: Optional[torch.Tensor], w: PackedTriMul):
+    """z [R, N, 128] -> a, b [R, 128, ld] (row-interleaved channel-major) and g [R, N, 128]."""
+    _need_cuda(z, mask_shard)
+    dev = _dev(z)
+    r, n, _ = z.shape
+    ld = _pad8(n)
+    x = torch.empty_like(z)
+    a = torch.zeros(r, 128, ld, dtype=BF16, device=z.device) if ld != n else torch.empty(r, 128, ld, dtype=BF16, device=z.device)
+    b = torch.zeros_like(a) if ld != n else torch.empty_like(a)
+    g = torch.empty_like(z)
+    m = None if mask_shard is None else mask_shard.to(torch.float32).contiguous()
+    rc = load().xfold_trimul_project_fwd(ctx(dev), _ptr(z), _ptr(m), r, n, C.byref(w.c), _ptr(x), _ptr(a), _ptr(b),
+                                         _ptr(g), ld, _stream(dev))
+    check(rc, dev, "xfold_trimul_project_fwd")
+    return a, b, g
+
+
+def stage_trimul_contract(a: torch.Tensor, b_full: torch.Tensor, n: int) -> torch.Tensor:
+    """o[i, c, j] = sum_k a[i, c, k] * b_full[j, c, k] over the first n entries of k."""
+    _need_cuda(a, b_full)
+    dev = _dev(a)
+    r, _, ld = a.shape
+    nj = b_full.shape[0]
+    ldo = _pad8(nj)
+    o = torch.empty(r, 128, ldo, dtype=BF16, device=a.device)
+    rc = load().xfold_trimul_contract_fwd(ctx(dev), _ptr(a), _ptr(b_full.contiguous()), r, nj, n, ld, _ptr(o), ldo,
+                                          _stream(dev))
+    check(rc, dev, "xfold_trimul_contract_fwd")
+    return o
+
+
+def stage_trimul_output(o: torch.Tensor, g: torch.Tensor, z: torch.Tensor, w: PackedTriMul) -> None:
+    _need_cuda(o, g, z)
+    dev = _dev(z)
+    r, n, _ = z.shape
+    x = torch.empty_like(z)
+    rc = load().xfold_trimul_output_fwd(ctx(dev), _ptr(o), o.shape[2], _ptr(g), r, n, C.byref(w.c), _ptr(x), _ptr(z),
+                                        _stream(dev))
+    check(rc, dev, "xfold_trimul_output_fwd")
+
+
+def stage_triattn_bias(z: torch.Tensor, w: PackedTriAttn, key_major_rows: bool):
+    """x = act_norm(z) and this shard's part of the key-major pair bias:
+    [4, N, R] when the rows are query rows, [4, R, pad8(N)] when they are key rows."""
+    _need_cuda(z)
+    dev = _dev(z)
+    r, n, _ = z.shape
+    x = torch.empty_like(z)
+    if key_major_rows:
+        pitch = _pad8(n)
+        bias = torch.zeros(4, r, pitch, dtype=BF16, device=z.device)
+        plane = r * pitch
+    else:
+        pitch = _pad8(r)
+        bias = torch.zeros(4, n, pitch, dtype=BF16, device=z.device)
+        plane = n * pitch
+    rc = load().xfold_triattn_bias_fwd(ctx(dev), _ptr(z), r, n, C.byref(w.c), _ptr(x), _ptr(bias), pitch, plane,
+                                       int(key_major_rows), _stream(dev))
+    check(rc, dev, "xfold_triattn_bias_fwd")
+    return x, (bias if key_major_rows else bias[..., :r])
+
+
+def stage_triattn_core(x: torch.Tensor, bias_t: torch.Tensor, mask_shard: Optional[torch.Tensor], w: PackedTriAttn,
+                       z: torch.Tensor) -> None:
+    _need_cuda(x, bias_t, mask_shard, z)
+    dev = _dev(z)
+    r, n, _ = z.shape
+    lib = load()
+    mext_bytes = C.c_size_t()
+    qkvg_bytes = lib.xfold_triattn_core_scratch_bytes(r, n, C.byref(mext_bytes))
+    qkvg = torch.empty(qkvg_bytes, dtype=torch.uint8, device=z.device)
+    mext = torch.empty(mext_bytes.value, dtype=torch.uint8, device=z.device)
+    m = None if mask_shard is None else mask_shard.to(torch.float32).contiguous()
+    bias_t = bias_t.contiguous()
+    assert bias_t.shape[0] == 4 and bias_t.shape[1] == n and bias_t.shape[2] % 8 == 0
+    rc = lib.xfold_triattn_core_fwd(ctx(dev), _ptr(x), _ptr(bias_t), bias_t.shape[2], _ptr(m), n, r, n, C.byref(w.c),
+                                    _ptr(qkvg), _ptr(mext), _ptr(z), _stream(dev))
+    check(rc, dev, "xfold_triattn_core_fwd")
+
+
+def stage_transition(x: torch.Tensor, w: PackedTransition) -> None:
+    transition_(x, w)
+
+
+def stage_pair_logits(z: torch.Tensor, w: PackedPairformerBlock) -> torch.Tensor:
+    """Key-major pair logits contributed by this shard's (query) rows: bf16 [16, N, R]."""
+    _need_cuda(z)
+    dev = _dev(z)
+    r, n, _ = z.shape
+    pitch = _pad8(r)
+    out = torch.zeros(16, n, pitch, dtype=BF16, device=z.device)
+    rc = load().xfold_pair_logits_fwd(ctx(dev), _ptr(z), r, n, _ptr(w.spl_g), _ptr(w.spl_b), _ptr(w.spl_w), _ptr(out),
+                                      pitch, n * pitch, 0, _stream(dev))
+    check(rc, dev, "xfold_pair_logits_fwd")
+    return out[..., :r]
+
+
+def stage_single_update(s: torch.Tensor, pl_t: torch.Tensor, seq_mask: Optional[torch.Tensor],
+                        w: PackedPairformerBlock) -> None:
+    _need_cuda(s, pl_t, seq_mask)
+    dev = _dev(s)
+    n = s.shape[0]
+    lib = load()
+    nbytes = lib.xfold_single_update_workspace_bytes(n)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=s.device)
+    pl_t = pl_t.contiguous()
+    sm = None if seq_mask is None else seq_mask.to(torch.float32).contiguous()
+    rc = lib.xfold_single_update_fwd(ctx(dev), _ptr(s), _ptr(pl_t), pl_t.shape[2], _ptr(sm), n, C.byref(w.c), _ptr(ws),
+                                     nbytes, _stream(dev))
+    check(rc, dev, "xfold_single_update_fwd")

@@ -1,0 +1,142 @@
+"""Pairformer block on a pair representation partitioned by token rows over the ranks of one
+process group (one process per GPU) -- the layout of the reference's 'dp' axis in the trunk
+(nn/d_pairformer.py:119-156, distribute_utils.py:101-128), taken one step further: the pair
+representation STAYS sharded through the whole block, TriangleMultiplication included (the
+reference's sharded TriMul, nn/d_triangle_multiplication.py:48-99, is written but not wired in).
+
+Per block and rank, with R = rows held by the rank and zT the row shard of the transposed pair
+representation (zT[j][i] = z[i][j]):
+
+    z   : TriMul outgoing        gather b rows            (all-gather, N*N*c / P elements per peer)
+    zT  : TriMul incoming        gather b rows            'ckj,cki->cij' on z is 'cik,cjk->cij' on zT
+    z   : TriAttn starting node  gather the pair bias     (4 * N * N bf16 in total)
+    zT  : TriAttn ending node    gather the pair bias, then pair Transition (token-local)
+    z   : pair logits, gathered; the single path is replicated on every rank (it is < 1 % of the work)
+
+with a distributed transpose (all-to-all of R x R_peer blocks) between the layouts, in place of the
+reference's two all-gathers of the whole pair representation per block (nn/d_pairformer.py:134-155).
+
+The arithmetic is delegated to a *stage backend*: ``CudaStages`` calls the sm_100a kernels through
+the C ABI; the CPU tests plug in a double built on the oracle to check the sharding algebra under
+gloo.  Nothing in this file computes on tensors itself except the layout glue.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .distribute_utils import ShardInfo
+
+
+def _exchange(send: List[torch.Tensor], recv: List[torch.Tensor], group) -> None:
+    """Pairwise exchange: send[q] goes to group rank q, recv[p] arrives from group rank p."""
+    me = dist.get_rank(group)
+    world = dist.get_world_size(group)
+    recv[me].copy_(send[me])
+    ops = []
+    for off in range(1, world):
+        dst, src = (me + off) % world, (me - off) % world
+        ops.append(dist.P2POp(dist.isend, send[dst], dist.get_global_rank(group, dst) if group is not None else dst,
+                              group))
+        ops.append(dist.P2POp(dist.irecv, recv[src], dist.get_global_rank(group, src) if group is not None else src,
+                              group))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+
+
+class RowSharding:
+    """Row partition of an N-token pair representation over a process group."""
+
+    def __init__(self, n_tokens: int, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n = n_tokens
+        info = ShardInfo(n_tokens, self.world)
+        self.sizes, self.slices = info.shard_size_list, info.shard_slice_list
+        self.rows = self.slices[self.rank]
+        self.r = self.sizes[self.rank]
+
+    # -- collectives on shards -------------------------------------------------------------------
+    def gather_rows(self, local: torch.Tensor) -> torch.Tensor:
+        """[R_me, ...] on every rank -> [N, ...] (ragged row counts allowed)."""
+        if self.world == 1:
+            return local
+        out = local.new_empty((self.n,) + tuple(local.shape[1:]))
+        if len(set(self.sizes)) == 1:
+            dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
+            return out
+        pad = max(self.sizes)
+        buf = local.new_zeros((pad,) + tuple(local.shape[1:]))
+        buf[: self.r] = local
+        parts = [torch.empty_like(buf) for _ in range(self.world)]
+        dist.all_gather(parts, buf, group=self.group)
+        for p, (sl, sz) in enumerate(zip(self.slices, self.sizes)):
+            out[sl] = parts[p][:sz]
+        return out
+
+    def gather_last_dim(self, local: torch.Tensor, pitch: int) -> torch.Tensor:
+        """[..., R_me] on every rank -> [..., pitch] whose first N entries are the concatenation."""
+        parts = self.gather_rows(local.movedim(-1, 0).contiguous()) if self.world > 1 else local.movedim(-1, 0)
+        out = local.new_zeros(tuple(local.shape[:-1]) + (pitch,))
+        out[..., : self.n] = parts.movedim(0, -1)
+        return out
+
+    def transpose(self, z: torch.Tensor) -> torch.Tensor:
+        """Row shard of z [R_me, N, c] -> row shard of z^T: out[j_local, i] = z_global[i, j_global]."""
+        if self.world == 1:
+            return z.transpose(0, 1).contiguous()
+        c = z.shape[-1]
+        send = [z[:, sl, :].transpose(0, 1).contiguous() for sl in self.slices]          # to q: [R_q, R_me, c]
+        recv = [z.new_empty((self.r, sz, c)) for sz in self.sizes]                       # from p: [R_me, R_p, c]
+        _exchange(send, recv, self.group)
+        return torch.cat(recv, dim=1)
+
+
+class CudaStages:
+    """Stage backend on the C ABI (sm_100a kernels)."""
+
+    def __init__(self):
+        from . import ops
+        self.ops = ops
+
+    def __getattr__(self, name):
+        return getattr(self.ops, "stage_" + name)
+
+
+def pairformer_block(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch.Tensor], pair_mask: torch.Tensor,
+                     pair_mask_t: torch.Tensor, seq_mask: Optional[torch.Tensor], w) -> tuple:
+    """One block.  z: this rank's rows [R, N, c] (updated, returned); s: replicated [N, c_s];
+    pair_mask / pair_mask_t: the full [N, N] mask and its transpose (replicated, float32)."""
+    n, rows = sh.n, sh.rows
+    ldq = (n + 7) // 8 * 8
+    # TriangleMultiplication, outgoing edges, on z
+    a, b, g = stages.trimul_project(z, pair_mask[rows], w.tri_out)
+    o = stages.trimul_contract(a, sh.gather_rows(b), n)
+    stages.trimul_output(o, g, z, w.tri_out)
+    # incoming edges: the same product on the transposed layout
+    zt = sh.transpose(z)
+    a, b, g = stages.trimul_project(zt, pair_mask_t[rows], w.tri_in)
+    o = stages.trimul_contract(a, sh.gather_rows(b), n)
+    stages.trimul_output(o, g, zt, w.tri_in)
+    del a, b, g, o
+    # TriangleAttention, starting node, on z: local rows are QUERY rows of the bias
+    z = sh.transpose(zt)
+    x, bias_loc = stages.triattn_bias(z, w.att_start, False)          # [4, N, R]
+    bias = sh.gather_last_dim(bias_loc, ldq)                          # [4, N, ldq]
+    stages.triattn_core(x, bias, pair_mask[rows], w.att_start, z)
+    # ending node on zT: local rows are KEY rows of the bias; mask rows as the reference passes them
+    zt = sh.transpose(z)
+    x, bias_loc = stages.triattn_bias(zt, w.att_end, True)            # [4, R, ldq]
+    bias = sh.gather_rows(bias_loc.transpose(0, 1).contiguous()).transpose(0, 1).contiguous()
+    stages.triattn_core(x, bias, pair_mask[rows], w.att_end, zt)
+    del x, bias, bias_loc
+    stages.transition(zt, w.pair_transition)
+    z = sh.transpose(zt)
+    if s is not None and w.with_single:
+        pl_loc = stages.pair_logits(z, w)                             # [16, N, R]
+        stages.single_update(s, sh.gather_last_dim(pl_loc, ldq), seq_mask, w)
+    return z, s

@@ -193,6 +193,43 @@ size_t xfold_pairformer_workspace_bytes(int N);
 int xfold_pairformer_block_fwd(xfold_ctx* ctx, void* z, void* s, const float* pair_mask, const float* seq_mask,
                                int N, const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
 
+/* ---- row-shard stages -------------------------------------------------------------------------
+ * The pieces of TriangleMultiplication / TriangleAttention on a block of R pair rows, for the
+ * multi-GPU block where the pair representation is partitioned by token rows
+ * (nn/d_pairformer.py:119-156, distribute_utils.py:101-128) and a collective sits between stages.
+ *
+ * a, b: bf16 [rows][128][ld], element (row i, channel c, k) at (i * 128 + c) * ld + k, so a rank's rows
+ * are one contiguous block and the all-gather of b (nn/d_triangle_multiplication.py:74-79) is a
+ * concatenation.  g: bf16 [R * N][128].  o: bf16 [R][128][ldo]. */
+int xfold_trimul_project_fwd(xfold_ctx* ctx, const void* z, const float* mask, int R, int N,
+                             const xfold_trimul_weights* w, void* x_scratch, void* a, void* b, void* g, int ld,
+                             void* stream);
+/* o[i][c][j] = sum_k a[i][c][k] * b_full[j][c][k]  ('cik,cjk->cij' on the row shard of a against all rows of b) */
+int xfold_trimul_contract_fwd(xfold_ctx* ctx, const void* a, const void* b_full, int R, int Nj, int K, int ld, void* o,
+                              int ldo, void* stream);
+/* z[R][N][128] += output_projection(center_norm(o)) * sigmoid(g)   (nn/d_triangle_multiplication.py:92-99) */
+int xfold_trimul_output_fwd(xfold_ctx* ctx, const void* o, int ldo, const void* g, int R, int N,
+                            const xfold_trimul_weights* w, void* x_scratch, void* z, void* stream);
+/* x = act_norm(z) for R rows and the pair bias these rows contribute (nn/d_attention.py:61-62), bf16:
+ * key_major_rows = 0: the rows are query rows x, biasT[h * plane + y * pitch + x_local];
+ * key_major_rows = 1: the rows are key rows,     biasT[h * plane + row_local * pitch + y]. */
+int xfold_triattn_bias_fwd(xfold_ctx* ctx, const void* z, int R, int N, const xfold_triattn_weights* w, void* x,
+                           void* biasT, int pitch, long long plane, int key_major_rows, void* stream);
+/* z[R][N][128] += output_projection(gated attention(x)) along the second axis; biasT: bf16 [4][N][ldq], key-major,
+ * gathered from all ranks; mask: float32, row b at mask + b * mask_ld. Scratch sizes from the function below. */
+size_t xfold_triattn_core_scratch_bytes(int R, int N, size_t* mext_bytes);
+int xfold_triattn_core_fwd(xfold_ctx* ctx, void* x, const void* biasT, int ldq, const float* mask, long long mask_ld,
+                           int R, int N, const xfold_triattn_weights* w, void* qkvg_scratch, void* mext_scratch, void* z,
+                           void* stream);
+/* Pair logits of the single path (nn/d_pairformer.py:158-160) for R rows, same layouts as the bias above (16 heads). */
+int xfold_pair_logits_fwd(xfold_ctx* ctx, const void* z, int R, int N, const float* ln_gamma, const float* ln_beta,
+                          const float* w16, void* plT, int pitch, long long plane, int key_major_rows, void* stream);
+/* single += AttentionPairBias(single, plT) ; single += Transition(single)   (nn/d_pairformer.py:162-169);
+ * plT: bf16 [16][N][ldq] key-major pair logits of the whole pair representation. */
+size_t xfold_single_update_workspace_bytes(int N);
+int xfold_single_update_fwd(xfold_ctx* ctx, void* s, const void* plT, int ldq, const float* seq_mask, int N,
+                            const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
