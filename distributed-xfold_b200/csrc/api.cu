@@ -679,4 +679,44 @@ int xfold_single_update_fwd(xfold_ctx* c, void* s, const void* plT, int ldq, con
   return single_update(c, (bf16*)s, (const bf16*)plT, ldq, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+/* ---- Transition without caller-provided scratch -------------------------------------------------
+ * Scratch for xfold_transition_static_fwd lives in the library image itself: one array per GPU that
+ * loads the library, kept until the process exits.  XFOLD_STATIC_SCRATCH_BYTES is its (fixed) size. */
+#define XFOLD_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_static_scratch[XFOLD_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[64] = {nullptr};  // device address of the array, per device ordinal
+
+size_t xfold_transition_static_max_bytes(void) { return XFOLD_STATIC_SCRATCH_BYTES; }
+
+int xfold_transition_static_fwd(xfold_ctx* c, void* x, long long rows, int C, int F, const xfold_transition_weights* w,
+                                void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  if (rows < 0 || C <= 0 || F <= 0) return fail(c, XFOLD_ERR_ARG, "transition (static scratch): bad shape");
+  const size_t need = xfold_transition_workspace_bytes(rows, C, F);
+  if (need > XFOLD_STATIC_SCRATCH_BYTES)
+    return fail(c, XFOLD_ERR_ARG,
+                "transition (static scratch): %lld rows x (C=%d + F=%d) need %zu bytes of scratch, the built-in "
+                "array holds %u; use xfold_transition_fwd with a caller-provided workspace",
+                rows, C, F, need, (unsigned)XFOLD_STATIC_SCRATCH_BYTES);
+  if (c->device < 0 || c->device >= 64) return fail(c, XFOLD_ERR_ARG, "transition (static scratch): device ordinal out of range");
+  if (!g_static_scratch_addr[c->device]) {
+    // first call on this device: resolve the device address of the array.  In host code the symbol
+    // g_static_scratch is only a handle, so it is never passed to a kernel directly.
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != c->device)
+      return fail(c, XFOLD_ERR_DEVICE, "transition (static scratch): device %d must be current (current: %d)", c->device, cur);
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p)
+      return fail(c, XFOLD_ERR_DEVICE, "transition (static scratch): cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_static_scratch_addr[c->device] = p;
+  }
+  const int prof = c->prof_on;  // event pairs are created on demand by the profiler: keep this path free of that
+  c->prof_on = 0;
+  const int rc = transition_fwd(c, (bf16*)x, rows, C, F, w, g_static_scratch_addr[c->device], XFOLD_STATIC_SCRATCH_BYTES,
+                                (cudaStream_t)stream);
+  c->prof_on = prof;
+  return rc;
+}
+
 }  // extern "C"

@@ -230,6 +230,26 @@ size_t xfold_single_update_workspace_bytes(int N);
 int xfold_single_update_fwd(xfold_ctx* ctx, void* s, const void* plT, int ldq, const float* seq_mask, int N,
                             const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
 
+/* ---- Transition for callers that cannot allocate device memory ------------------------------------
+ * (This entry point has no counterpart in the reference.)
+ * Same operation and result as xfold_transition_fwd, but the scratch (normalised input and SwiGLU
+ * hidden activations) is a fixed array inside the library instead of a caller workspace.  It is meant
+ * for hosts that are handed input/output buffers but may not call cudaMalloc themselves, e.g. a plugin
+ * running inside another runtime's memory arena, or a latency path where allocation is forbidden.
+ *  - Limit: xfold_transition_workspace_bytes(rows, C, F) must not exceed
+ *    xfold_transition_static_max_bytes() (16 MiB: 4096 rows of the single representation, C 384 / F 1536,
+ *    or 13107 pair tokens with C 128 / F 512); larger calls are rejected with XFOLD_ERR_ARG.
+ *  - Every GPU that loads the library carries the array until the process exits.
+ *  - The first call on a device looks up the array's device address (the context's device must be
+ *    current); make that first call before starting any stream capture.
+ *  - No cudaMalloc / cudaFree or other allocating call is made.  Nothing in the scratch has to start
+ *    from zero: each call overwrites every element it later reads, so stale contents of an earlier call
+ *    are harmless.  All calls share the one array: two calls that overlap on the GPU (different streams)
+ *    race on it; serialise them. */
+size_t xfold_transition_static_max_bytes(void);
+int xfold_transition_static_fwd(xfold_ctx* ctx, void* x, long long rows, int C, int F,
+                                const xfold_transition_weights* w, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
