@@ -73,6 +73,9 @@ SIGNATURES = {
     "xfold_pair_logits_fwd": (ci, [vp, vp, ci, ci, vp, vp, vp, vp, ci, ll, ci, vp]),
     "xfold_single_update_workspace_bytes": (sz, [ci]),
     "xfold_single_update_fwd": (ci, [vp, vp, vp, ci, vp, ci, C.POINTER(PairformerWeights), vp, sz, vp]),
+    "xfold_triangle_multiplication_update_fwd": (ci, [vp, vp, vp, vp, ci, ci, C.POINTER(TriMulWeights), vp, sz, vp]),
+    "xfold_triangle_attention_update_fwd": (ci, [vp, vp, vp, vp, ci, ci, C.POINTER(TriAttnWeights), vp, sz, vp]),
+    "xfold_transition_update_fwd": (ci, [vp, vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp, sz, vp]),
     "xfold_transition_static_max_bytes": (sz, []),
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),
     "xfold_pairformer_workspace_bytes": (sz, [ci]),

@@ -244,10 +244,12 @@ static int trimul_contract(Ctx* c, const bf16* a_, const bf16* b_, int Ri, int N
 
 // z (+)= Linear(LN_c(o)) * sigmoid(g); o: [R][128][ldo]; x: scratch [R*N][128]
 static int trimul_output(Ctx* c, const bf16* o, int ldo, const bf16* g, int R, int N, const xfold_trimul_weights* w,
-                         bf16* x, bf16* z, cudaStream_t st) {
+                         bf16* x, bf16* z, cudaStream_t st, bf16* upd = nullptr) {
   int rc = launch_cm_ln(c, o, ldo, (long long)128 * ldo, R, N, x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
   if (rc) return rc;
-  return linear_gate_resid(c, x, 128, (long long)R * N, 128, (const bf16*)w->w_out, 128, g, 128, 0, z, 128, z, 128, st);
+  // upd given: write the update alone there and leave z untouched; else z += update
+  return linear_gate_resid(c, x, 128, (long long)R * N, 128, (const bf16*)w->w_out, 128, g, 128, 0, upd ? nullptr : z, 128,
+                           upd ? upd : z, 128, st);
 }
 
 struct TriMulWs {
@@ -271,7 +273,7 @@ static TriMulWs carve_trimul(void* ws, size_t cap, int N) {
 }
 
 static int trimul_fwd(Ctx* c, bf16* z, const float* mask, int N, int outgoing, const xfold_trimul_weights* w, void* ws,
-                      size_t ws_bytes, cudaStream_t st) {
+                      size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr) {
   if (!z || !w || !w->w_in || !w->w_out) return fail(c, XFOLD_ERR_ARG, "trimul: null argument");
   if (N <= 0) return XFOLD_OK;
   TriMulWs W = carve_trimul(ws, ws_bytes, N);
@@ -281,7 +283,7 @@ static int trimul_fwd(Ctx* c, bf16* z, const float* mask, int N, int outgoing, c
   if (rc) return rc;
   rc = trimul_contract(c, outgoing ? W.a : W.b, outgoing ? W.b : W.a, N, N, N, W.ld, W.o, W.ld, st);
   if (rc) return rc;
-  return trimul_output(c, W.o, W.ld, W.g, N, N, w, W.x, z, st);
+  return trimul_output(c, W.o, W.ld, W.g, N, N, w, W.x, z, st, upd);
 }
 
 struct TriAttnWs {
@@ -319,7 +321,8 @@ static int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn
 // z (+)= out_proj(gated attention(x)) for R batch rows (sequence length N); biasT: bf16 [4][N][ldq] key-major.
 // transposed: the R x N token grid is stored [N][R] (sequence index outermost), used by the single-GPU ending node.
 static int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
-                        int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st) {
+                        int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st,
+                        bf16* upd = nullptr) {
   const long long M = (long long)R * N;
   int rc = linear_plain(c, x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, qkvg, 512, st);
   if (rc) return rc;
@@ -329,11 +332,12 @@ static int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float
   rc = launch_attention2(c, qkvg, 512, N, R, transposed, 0, 128, 256, 384, 4, biasT, ldq, mext, R, x, seq_stride,
                          batch_stride, st);
   if (rc) return rc;
-  return linear_gate_resid(c, x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, z, 128, z, 128, st);
+  return linear_gate_resid(c, x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, upd ? nullptr : z, 128,
+                           upd ? upd : z, 128, st);
 }
 
 static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose, const xfold_triattn_weights* w, void* ws,
-                       size_t ws_bytes, cudaStream_t st) {
+                       size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr) {
   if (!z || !w || !w->w_qkvg || !w->w_out || !w->w_bias) return fail(c, XFOLD_ERR_ARG, "triattn: null argument");
   if (N <= 0) return XFOLD_OK;
   TriAttnWs W = carve_triattn(ws, ws_bytes, N, N);
@@ -341,11 +345,11 @@ static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose,
   // both nodes use bias(q, k) = projection of token (q, k), not transposed for the ending node
   int rc = triattn_bias(c, z, N, N, w, W.x, W.nbT, W.ldq, (long long)N * W.ldq, 0, st);
   if (rc) return rc;
-  return triattn_core(c, W.x, W.nbT, W.ldq, mask, N, N, N, transpose, w, W.qkvg, W.mext, z, st);
+  return triattn_core(c, W.x, W.nbT, W.ldq, mask, N, N, N, transpose, w, W.qkvg, W.mext, z, st, upd);
 }
 
 static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
-                          size_t ws_bytes, cudaStream_t st) {
+                          size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr) {
   if (!x || !w || !w->w1_packed || !w->w2) return fail(c, XFOLD_ERR_ARG, "transition: null argument");
   if (rows <= 0) return XFOLD_OK;
   Carver cv(ws, ws_bytes);
@@ -357,7 +361,7 @@ static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const x
   if (rc) return rc;
   rc = linear_swiglu(c, xn, C, rows, C, (const bf16*)w->w1_packed, F, h, F, st);
   if (rc) return rc;
-  return linear_gate_resid(c, h, F, rows, F, (const bf16*)w->w2, C, nullptr, 0, 0, x, C, x, C, st);
+  return linear_gate_resid(c, h, F, rows, F, (const bf16*)w->w2, C, nullptr, 0, 0, upd ? nullptr : x, C, upd ? upd : x, C, st);
 }
 
 struct ApbWs {
@@ -677,6 +681,25 @@ int xfold_single_update_fwd(xfold_ctx* c, void* s, const void* plT, int ldq, con
                             const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream) {
   if (!c || !s || !plT || !w) return XFOLD_ERR_ARG;
   return single_update(c, (bf16*)s, (const bf16*)plT, ldq, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+/* ---- update-only variants: the module forwards of the reference RETURN the update and leave the
+ * residual add to the caller (e.g. nn/d_pairformer.py:122); these write it to `update` and do not touch z. */
+int xfold_triangle_multiplication_update_fwd(xfold_ctx* c, const void* z, void* update, const float* mask, int N,
+                                             int outgoing, const xfold_trimul_weights* w, void* ws, size_t ws_bytes,
+                                             void* stream) {
+  if (!c || !update) return XFOLD_ERR_ARG;
+  return trimul_fwd(c, (bf16*)const_cast<void*>(z), mask, N, outgoing, w, ws, ws_bytes, (cudaStream_t)stream, (bf16*)update);
+}
+int xfold_triangle_attention_update_fwd(xfold_ctx* c, const void* z, void* update, const float* mask, int N, int transpose,
+                                        const xfold_triattn_weights* w, void* ws, size_t ws_bytes, void* stream) {
+  if (!c || !update) return XFOLD_ERR_ARG;
+  return triattn_fwd(c, (bf16*)const_cast<void*>(z), mask, N, transpose, w, ws, ws_bytes, (cudaStream_t)stream, (bf16*)update);
+}
+int xfold_transition_update_fwd(xfold_ctx* c, const void* x, void* update, long long rows, int C, int F,
+                                const xfold_transition_weights* w, void* ws, size_t ws_bytes, void* stream) {
+  if (!c || !update) return XFOLD_ERR_ARG;
+  return transition_fwd(c, (bf16*)const_cast<void*>(x), rows, C, F, w, ws, ws_bytes, (cudaStream_t)stream, (bf16*)update);
 }
 
 /* ---- Transition without caller-provided scratch -------------------------------------------------

@@ -143,7 +143,7 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
           for (int h = 0; h < H; ++h) acc[h] = warp_sum(acc[h]);
 #pragma unroll
           for (int h = 0; h < H; ++h)
-            if (lane == h) {
+            if (lane == (h & 31)) {
               if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(acc[h]);
               else proj[(long long)h * proj_plane + pidx[j]] = acc[h];
             }

@@ -230,6 +230,18 @@ size_t xfold_single_update_workspace_bytes(int N);
 int xfold_single_update_fwd(xfold_ctx* ctx, void* s, const void* plT, int ldq, const float* seq_mask, int N,
                             const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
 
+/* ---- update-only variants ----------------------------------------------------------------------
+ * The reference's module forwards return the update and the caller adds it (`pair += module(pair, ...)`,
+ * nn/d_pairformer.py:122-146).  These write the update to `update` (same shape as z) and leave z untouched. */
+int xfold_triangle_multiplication_update_fwd(xfold_ctx* ctx, const void* z, void* update, const float* mask, int N,
+                                             int outgoing, const xfold_trimul_weights* w, void* ws, size_t ws_bytes,
+                                             void* stream);
+int xfold_triangle_attention_update_fwd(xfold_ctx* ctx, const void* z, void* update, const float* mask, int N,
+                                        int transpose, const xfold_triattn_weights* w, void* ws, size_t ws_bytes,
+                                        void* stream);
+int xfold_transition_update_fwd(xfold_ctx* ctx, const void* x, void* update, long long rows, int C, int F,
+                                const xfold_transition_weights* w, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- Transition for callers that cannot allocate device memory ------------------------------------
  * (This entry point has no counterpart in the reference.)
  * Same operation and result as xfold_transition_fwd, but the scratch (normalised input and SwiGLU

@@ -113,3 +113,15 @@ def test_batched_contract(ops, ch, mi, nj, kk):
     ops.synchronize_and_check()
     ref = torch.einsum("cik,cjk->cij", a.float(), b.float())
     assert relf(out.float().cpu(), ref) < 4e-3
+
+
+def test_layernorm_fused_projection_64(ops):
+    """64 outputs (the diffusion transformer's pair logits for one super-block: 4 blocks x 16 heads)."""
+    rows, C, H = 1500, 128, 64
+    x = rnd(rows, C, seed=17)
+    w = torch.randn(H, C, generator=torch.Generator().manual_seed(4)) / 11
+    g = torch.rand(C, generator=torch.Generator().manual_seed(5)) + 0.5
+    _, proj = ops.layernorm(x.cuda(), g.cuda(), None, proj_w=w.cuda(), want_y=False)
+    ops.synchronize_and_check()
+    ref = torch.nn.functional.layer_norm(x.float(), (C,), g, None, 1e-5)
+    assert relf(proj.cpu(), (ref @ w.T).T) < 1e-4
