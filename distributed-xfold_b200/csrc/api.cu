@@ -183,8 +183,8 @@ static inline int pad8(int n) { return (n + 7) & ~7; }
 // A rank's rows are one contiguous block, so the all-gather of b over the row-shard group is a plain
 // concatenation, and the per-channel operand of the contraction is a strided 2-D slice for TMA.
 static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N, int transposed_store,
-                          const xfold_trimul_weights* w, bf16* x, bf16* a_out, bf16* b_out, bf16* g, int ld,
-                          cudaStream_t st) {
+                          const xfold_trimul_weights* w, bf16* x, bf16* a_out, bf16* b_out, bf16* g, long long chan_stride,
+                          long long row_stride, cudaStream_t st) {
   const long long M = (long long)R * N;
   int rc = launch_ln_rows(c, z, 128, x, 128, M, 128, w->ln_in_gamma, w->ln_in_beta, 1e-5f, 0, nullptr, nullptr, 0,
                           nullptr, nullptr, 0, st);
@@ -211,8 +211,8 @@ static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N
   a.out_a = a_out;
   a.out_b = b_out;
   a.out_g = g;
-  a.cm_chan_stride = ld;
-  a.cm_ld = 128 * ld;
+  a.cm_chan_stride = chan_stride;
+  a.cm_ld = row_stride;
   a.ntok = N;
   a.mask = mask;
   a.status = c->d_status;
@@ -220,12 +220,13 @@ static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N
 }
 
 // o[i][c][j] = sum_k a[i][c][k] * b[j][c][k]   (a: Ri rows, b: Nj rows, both [.][128][ld]; o: [Ri][128][ldo])
-static int trimul_contract(Ctx* c, const bf16* a_, const bf16* b_, int Ri, int Nj, int K, int ld, bf16* o, int ldo,
-                           cudaStream_t st) {
-  if ((ld & 7) || (ldo & 7)) return fail(c, XFOLD_ERR_ARG, "contract: leading dimensions must be multiples of 8");
+// (chan, row) strides in elements: row-interleaved [rows][128][ld] has (ld, 128*ld); channel-major [128][rows][ld] has (rows*ld, ld)
+static int trimul_contract(Ctx* c, const bf16* a_, long long a_cs, long long a_rs, const bf16* b_, long long b_cs,
+                           long long b_rs, int Ri, int Nj, int K, bf16* o, long long o_cs, long long o_rs, cudaStream_t st) {
+  if (((a_cs | a_rs | b_cs | b_rs | o_cs | o_rs) & 7)) return fail(c, XFOLD_ERR_ARG, "contract: strides must be multiples of 8");
   CUtensorMap tA, tB;
-  if (!make_tmap_bf16_3d(&tA, a_, K, Ri, 128, (uint64_t)128 * ld, ld, 64, 128, 1) ||
-      !make_tmap_bf16_3d(&tB, b_, K, Nj, 128, (uint64_t)128 * ld, ld, 64, 256, 1))
+  if (!make_tmap_bf16_3d(&tA, a_, K, Ri, 128, a_rs, a_cs, 64, 128, 1) ||
+      !make_tmap_bf16_3d(&tB, b_, K, Nj, 128, b_rs, b_cs, 64, 256, 1))
     return fail(c, XFOLD_ERR_ARG, "contract: cannot encode tensor maps");
   GemmArgs a;
   a.M = Ri;
@@ -236,16 +237,16 @@ static int trimul_contract(Ctx* c, const bf16* a_, const bf16* b_, int Ri, int N
   a.tiles_m = (Ri + 127) / 128;
   a.tiles_n = (Nj + 255) / 256;
   a.out = o;
-  a.ldo = (long long)128 * ldo;
-  a.out_batch_stride = ldo;
+  a.ldo = o_rs;
+  a.out_batch_stride = o_cs;
   a.status = c->d_status;
   return launch_gemm(c, EPI_PLAIN, 256, tA, tB, a, st);
 }
 
 // z (+)= Linear(LN_c(o)) * sigmoid(g); o: [R][128][ldo]; x: scratch [R*N][128]
-static int trimul_output(Ctx* c, const bf16* o, int ldo, const bf16* g, int R, int N, const xfold_trimul_weights* w,
-                         bf16* x, bf16* z, cudaStream_t st, bf16* upd = nullptr) {
-  int rc = launch_cm_ln(c, o, ldo, (long long)128 * ldo, R, N, x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
+static int trimul_output(Ctx* c, const bf16* o, long long o_cs, long long o_rs, const bf16* g, int R, int N,
+                         const xfold_trimul_weights* w, bf16* x, bf16* z, cudaStream_t st, bf16* upd = nullptr) {
+  int rc = launch_cm_ln(c, o, o_cs, o_rs, R, N, x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
   if (rc) return rc;
   // upd given: write the update alone there and leave z untouched; else z += update
   return linear_gate_resid(c, x, 128, (long long)R * N, 128, (const bf16*)w->w_out, 128, g, 128, 0, upd ? nullptr : z, 128,
@@ -279,11 +280,13 @@ static int trimul_fwd(Ctx* c, bf16* z, const float* mask, int N, int outgoing, c
   TriMulWs W = carve_trimul(ws, ws_bytes, N);
   if (!ws || W.bytes > ws_bytes) return fail(c, XFOLD_ERR_ARG, "trimul: workspace too small (%zu < %zu)", ws_bytes, W.bytes);
   // incoming: a and b are stored transposed, so that o[i][c][j] = sum_k bT[i][c][k] aT[j][c][k] is the same product
-  int rc = trimul_project(c, z, mask, N, N, outgoing ? 0 : 1, w, W.x, W.a, W.b, W.g, W.ld, st);
+  // one GPU: plain channel-major planes [128][N][ld] (rows of a tile are 2 KB apart, best DRAM locality)
+  const long long cs = (long long)N * W.ld, rs = W.ld;
+  int rc = trimul_project(c, z, mask, N, N, outgoing ? 0 : 1, w, W.x, W.a, W.b, W.g, cs, rs, st);
   if (rc) return rc;
-  rc = trimul_contract(c, outgoing ? W.a : W.b, outgoing ? W.b : W.a, N, N, N, W.ld, W.o, W.ld, st);
+  rc = trimul_contract(c, outgoing ? W.a : W.b, cs, rs, outgoing ? W.b : W.a, cs, rs, N, N, N, W.o, cs, rs, st);
   if (rc) return rc;
-  return trimul_output(c, W.o, W.ld, W.g, N, N, w, W.x, z, st, upd);
+  return trimul_output(c, W.o, cs, rs, W.g, N, N, w, W.x, z, st, upd);
 }
 
 struct TriAttnWs {
@@ -303,22 +306,20 @@ static TriAttnWs carve_triattn(void* ws, size_t cap, int R, int N) {
   return w;
 }
 
-// x = LN(z) for a block of R rows, plus the pair bias those rows contribute, written bf16:
-//   key_major_rows == 0: rows are QUERY rows x: biasT[h][y][x_local] (walks the tokens column by column)
-//   key_major_rows == 1: rows are KEY rows:      biasT[h][row_local][y]  (row-major walk)
-// pitch is the row pitch of the destination (elements), plane its per-head stride.
-static int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weights* w, bf16* x, bf16* biasT,
-                        int pitch, long long plane, int key_major_rows, cudaStream_t st) {
+// x = LN(z) for a block of R rows, plus the pair bias those rows contribute, bf16, query-major [h][q][k]:
+//   rows_are_keys == 0: the rows are QUERY rows:  bias[h * plane + row_local * pitch + y]      (row-major walk)
+//   rows_are_keys == 1: the rows are KEY rows x:  bias[h * plane + y * pitch + x_local]        (column-by-column walk)
+static int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weights* w, bf16* x, bf16* bias,
+                        int pitch, long long plane, int rows_are_keys, cudaStream_t st) {
   const long long M = (long long)R * N;
-  if (!key_major_rows)
+  if (!rows_are_keys)
     return launch_ln_rows(c, z, 128, x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, nullptr, plane, nullptr,
-                          nullptr, 0, st, biasT, R, N, pitch);
-  // linear walk with a padded pitch: "inner" = N tokens per row, source row = prow itself
+                          nullptr, 0, st, bias, -N, 0, pitch);
   return launch_ln_rows(c, z, 128, x, 128, M, 128, w->ln_gamma, w->ln_beta, 1e-5f, 4, w->w_bias, nullptr, plane, nullptr,
-                        nullptr, 0, st, biasT, -N, 0, pitch);
+                        nullptr, 0, st, bias, R, N, pitch);
 }
 
-// z (+)= out_proj(gated attention(x)) for R batch rows (sequence length N); biasT: bf16 [4][N][ldq] key-major.
+// z (+)= out_proj(gated attention(x)) for R batch rows (sequence length N); biasT: bf16 [4][N][ldq], [h][query][key].
 // transposed: the R x N token grid is stored [N][R] (sequence index outermost), used by the single-GPU ending node.
 static int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
                         int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st,
@@ -383,7 +384,7 @@ static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
   return cv->off;
 }
 
-// pair_bias: float32 [H][S][S] (query-major), or, when pair_biasT is given, bf16 [H][S][pad8(S)] key-major
+// pair_bias: float32 [H][S][S], or, when pair_biasT is given, the same as bf16 [H][S][pad8(S)] (both [h][query][key])
 static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
                         const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
@@ -418,7 +419,7 @@ static size_t single_ws_bytes(int N) {
 }
 
 // single += AttentionPairBias(single, pair logits) ; single += Transition(single)   (nn/d_pairformer.py:162-169)
-// plT: bf16 [16][N][ldq] key-major pair logits.
+// plT: bf16 [16][N][ldq] pair logits, [h][query][key].
 static int single_update(Ctx* c, bf16* s, const bf16* plT, int ldq, const float* seq_mask, int N,
                          const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, cudaStream_t st) {
   Carver cv(ws, ws_bytes);
@@ -466,7 +467,7 @@ static int pairformer_fwd(Ctx* c, bf16* z, bf16* s, const float* pair_mask, cons
   if (!cv.ok()) return fail(c, XFOLD_ERR_ARG, "pairformer: workspace too small for the single path");
   const long long M = (long long)N * N;
   if ((rc = launch_ln_rows(c, z, 128, nullptr, 128, M, 128, w->spl_ln_gamma, w->spl_ln_beta, 1e-5f, 16, w->spl_w, nullptr,
-                           (long long)N * ldq, nullptr, nullptr, 0, st, pl, N, N, ldq))) return rc;
+                           (long long)N * ldq, nullptr, nullptr, 0, st, pl, -N, 0, ldq))) return rc;
   return single_update(c, s, pl, ldq, seq_mask, N, w, rest, single_ws_bytes(N), st);
 }
 
@@ -640,22 +641,26 @@ int xfold_trimul_project_fwd(xfold_ctx* c, const void* z, const float* mask, int
                              void* x_scratch, void* a, void* b, void* g, int ld, void* stream) {
   if (!c || !z || !w || !x_scratch || !a || !b || !g) return XFOLD_ERR_ARG;
   if (ld < N || (ld & 7)) return fail(c, XFOLD_ERR_ARG, "trimul project: ld must be >= N and a multiple of 8");
-  return trimul_project(c, (const bf16*)z, mask, R, N, 0, w, (bf16*)x_scratch, (bf16*)a, (bf16*)b, (bf16*)g, ld, (cudaStream_t)stream);
+  return trimul_project(c, (const bf16*)z, mask, R, N, 0, w, (bf16*)x_scratch, (bf16*)a, (bf16*)b, (bf16*)g, ld,
+                        (long long)128 * ld, (cudaStream_t)stream);
 }
 int xfold_trimul_contract_fwd(xfold_ctx* c, const void* a, const void* b_full, int R, int Nj, int K, int ld, void* o, int ldo,
                               void* stream) {
   if (!c || !a || !b_full || !o) return XFOLD_ERR_ARG;
-  return trimul_contract(c, (const bf16*)a, (const bf16*)b_full, R, Nj, K, ld, (bf16*)o, ldo, (cudaStream_t)stream);
+  if ((ld & 7) || (ldo & 7)) return fail(c, XFOLD_ERR_ARG, "contract: leading dimensions must be multiples of 8");
+  return trimul_contract(c, (const bf16*)a, ld, (long long)128 * ld, (const bf16*)b_full, ld, (long long)128 * ld, R, Nj, K,
+                         (bf16*)o, ldo, (long long)128 * ldo, (cudaStream_t)stream);
 }
 int xfold_trimul_output_fwd(xfold_ctx* c, const void* o, int ldo, const void* g, int R, int N, const xfold_trimul_weights* w,
                             void* x_scratch, void* z, void* stream) {
   if (!c || !o || !g || !w || !x_scratch || !z) return XFOLD_ERR_ARG;
-  return trimul_output(c, (const bf16*)o, ldo, (const bf16*)g, R, N, w, (bf16*)x_scratch, (bf16*)z, (cudaStream_t)stream);
+  return trimul_output(c, (const bf16*)o, ldo, (long long)128 * ldo, (const bf16*)g, R, N, w, (bf16*)x_scratch, (bf16*)z,
+                       (cudaStream_t)stream);
 }
 int xfold_triattn_bias_fwd(xfold_ctx* c, const void* z, int R, int N, const xfold_triattn_weights* w, void* x, void* biasT,
-                           int pitch, long long plane, int key_major_rows, void* stream) {
+                           int pitch, long long plane, int rows_are_keys, void* stream) {
   if (!c || !z || !w || !x || !biasT) return XFOLD_ERR_ARG;
-  return triattn_bias(c, (const bf16*)z, R, N, w, (bf16*)x, (bf16*)biasT, pitch, plane, key_major_rows, (cudaStream_t)stream);
+  return triattn_bias(c, (const bf16*)z, R, N, w, (bf16*)x, (bf16*)biasT, pitch, plane, rows_are_keys, (cudaStream_t)stream);
 }
 size_t xfold_triattn_core_scratch_bytes(int R, int N, size_t* mext_bytes) {
   if (mext_bytes) *mext_bytes = (size_t)R * ((N + 127) / 128) * 4096;
@@ -669,11 +674,11 @@ int xfold_triattn_core_fwd(xfold_ctx* c, void* x, const void* biasT, int ldq, co
                       (bf16*)mext_scratch, (bf16*)z, (cudaStream_t)stream);
 }
 int xfold_pair_logits_fwd(xfold_ctx* c, const void* z, int R, int N, const float* ln_gamma, const float* ln_beta,
-                          const float* w16, void* plT, int pitch, long long plane, int key_major_rows, void* stream) {
+                          const float* w16, void* plT, int pitch, long long plane, int rows_are_keys, void* stream) {
   if (!c || !z || !w16 || !plT) return XFOLD_ERR_ARG;
   const long long M = (long long)R * N;
   return launch_ln_rows(c, (const bf16*)z, 128, nullptr, 128, M, 128, ln_gamma, ln_beta, 1e-5f, 16, w16, nullptr, plane,
-                        nullptr, nullptr, 0, (cudaStream_t)stream, (bf16*)plT, key_major_rows ? -N : R, key_major_rows ? 0 : N,
+                        nullptr, nullptr, 0, (cudaStream_t)stream, (bf16*)plT, rows_are_keys ? R : -N, rows_are_keys ? N : 0,
                         pitch);
 }
 size_t xfold_single_update_workspace_bytes(int N) { return single_ws_bytes(N); }

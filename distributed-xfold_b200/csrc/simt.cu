@@ -153,6 +153,159 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Width-128 LayerNorm (the pair representation: ~1M rows per call at N = 1024).  Sixteen lanes share
+// a row (one 16-byte load each, so a warp moves two rows per request), gamma / beta live in
+// registers, the reductions take 4 shuffles, and SLOTS row pairs are in flight per warp.
+// Same arguments and semantics as ln_rows_kernel.
+// ---------------------------------------------------------------------------------------------
+template <int H>
+__global__ void __launch_bounds__(256, 3)
+ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, long long ldy, long long rows,
+             const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+             const float* __restrict__ pw, float* __restrict__ proj, long long proj_plane,
+             const bf16* __restrict__ mod_scale, const bf16* __restrict__ mod_shift, int mod_rows,
+             bf16* __restrict__ proj_bf16, int trav_inner, int trav_outer, int proj_pitch) {
+  constexpr int SLOTS = (H == 0) ? 4 : (H == 4 ? 2 : 1);
+  extern __shared__ float s_pw[];  // H x 128 projection weights
+  if constexpr (H > 0) {
+    for (int i = threadIdx.x; i < H * 128; i += blockDim.x) s_pw[i] = pw[i];
+    __syncthreads();
+  }
+  const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
+  const int c0 = l16 * 8;
+  float gm[8], bt[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    gm[e] = gamma ? gamma[c0 + e] : 1.f;
+    bt[e] = beta ? beta[c0 + e] : 0.f;
+  }
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long base = warp_global * 2; base < rows; base += nwarps * 2 * SLOTS) {
+    uint4 raw[SLOTS];
+    long long srow[SLOTS], pidx[SLOTS];
+    bool valid[SLOTS];
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) {
+      const long long prow = base + (long long)j * nwarps * 2 + half;
+      valid[j] = prow < rows;
+      const long long inner = trav_inner > 0 ? trav_inner : -trav_inner;
+      srow[j] = trav_inner > 0 ? (prow % inner) * trav_outer + prow / inner : prow;
+      pidx[j] = trav_inner != 0 ? (prow / inner) * proj_pitch + prow % inner : prow;
+      raw[j] = make_uint4(0, 0, 0, 0);
+      if (valid[j]) raw[j] = *reinterpret_cast<const uint4*>(x + srow[j] * ldx + c0);
+    }
+#pragma unroll
+    for (int j = 0; j < SLOTS; ++j) {
+      const uint32_t w4[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+      float v[8];
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        v[2 * e] = bf16_lo(w4[e]);
+        v[2 * e + 1] = bf16_hi(w4[e]);
+        s += v[2 * e] + v[2 * e + 1];
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s * (1.f / 128);
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[e] -= mean;
+        ss += v[e] * v[e];
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rstd = rsqrtf(ss * (1.f / 128) + eps);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = fmaf(v[e] * rstd, gm[e], bt[e]);
+      if (mod_scale && valid[j]) {
+        const long long mr = srow[j] % mod_rows;
+        const uint4 a = *reinterpret_cast<const uint4*>(mod_scale + mr * 128 + c0);
+        const uint4 b = *reinterpret_cast<const uint4*>(mod_shift + mr * 128 + c0);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          v[2 * e] = sigmoidf_fast(bf16_lo(aw[e])) * v[2 * e] + bf16_lo(bw[e]);
+          v[2 * e + 1] = sigmoidf_fast(bf16_hi(aw[e])) * v[2 * e + 1] + bf16_hi(bw[e]);
+        }
+      }
+      if (y && valid[j]) {
+        uint4 u;
+        u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+        u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(y + srow[j] * ldy + c0) = u;
+      }
+      if constexpr (H > 0) {
+#pragma unroll
+        for (int hb = 0; hb < H; hb += 16) {
+          constexpr int G = (H < 16) ? H : 16;  // heads reduced together over the 16 lanes of a row
+          float acc[G];
+#pragma unroll
+          for (int h = 0; h < G; ++h) {
+            const float4 w0 = *reinterpret_cast<const float4*>(s_pw + (hb + h) * 128 + c0);
+            const float4 w1 = *reinterpret_cast<const float4*>(s_pw + (hb + h) * 128 + c0 + 4);
+            acc[h] = v[0] * w0.x + v[1] * w0.y + v[2] * w0.z + v[3] * w0.w + v[4] * w1.x + v[5] * w1.y + v[6] * w1.z +
+                     v[7] * w1.w;
+          }
+          // recursive halving over lane bits 3..0: the lane keeps the half of the heads its bit selects
+          int nkeep = G;
+#pragma unroll
+          for (int off = 8; off > 0; off >>= 1) {
+            if (nkeep > 1) {
+              nkeep >>= 1;
+              const bool upper = (l16 & off) != 0;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (i < nkeep) {
+                  const float send = upper ? acc[i] : acc[i + nkeep];
+                  const float keep = upper ? acc[i + nkeep] : acc[i];
+                  acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+                }
+              }
+            } else {
+              acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], off);
+            }
+          }
+          // G = 16: head = l16 (bits 3..0 each picked a half); G = 4: head = l16 >> 2, shared by 4 lanes
+          const int hsel = (G == 16) ? (((l16 >> 3) & 1) * 8 + ((l16 >> 2) & 1) * 4 + ((l16 >> 1) & 1) * 2 + (l16 & 1))
+                                     : (((l16 >> 3) & 1) * 2 + ((l16 >> 2) & 1));
+          const bool writer = (G == 16) ? true : ((l16 & 3) == 0);
+          if (writer && valid[j]) {
+            const long long o = (long long)(hb + hsel) * proj_plane + pidx[j];
+            if (proj_bf16) proj_bf16[o] = __float2bfloat16(acc[0]);
+            else proj[o] = acc[0];
+          }
+        }
+      }
+    }
+  }
+}
+
+static int launch_ln128(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, const float* g,
+                        const float* b, float eps, int H, const float* pw, float* proj, long long plane,
+                        const bf16* msc, const bf16* msh, int mod_rows, bf16* pbf, int tin, int tout, int tpitch,
+                        cudaStream_t st) {
+  if ((ldx & 7) || (ldy & 7)) return fail(c, XFOLD_ERR_ARG, "layernorm(128): row strides must be multiples of 8 elements");
+  const int slots = (H == 0) ? 4 : (H == 4 ? 2 : 1);
+  long long blocks = (rows + 16 * slots - 1) / (16 * slots);  // 8 warps x 2 rows x slots per pass
+  const long long cap = (long long)c->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks <= 0) return XFOLD_OK;
+  const size_t sm = (size_t)H * 128 * sizeof(float);
+  ProfScope ps(c, XFOLD_K_LAYERNORM, st);
+  switch (H) {
+    case 0: ln128_kernel<0><<<(int)blocks, 256, sm, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    case 4: ln128_kernel<4><<<(int)blocks, 256, sm, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    case 16: ln128_kernel<16><<<(int)blocks, 256, sm, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    case 64: ln128_kernel<64><<<(int)blocks, 256, sm, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
+    default: return fail(c, XFOLD_ERR_ARG, "layernorm: fused projection supports 0, 4, 16 or 64 outputs, got %d", H);
+  }
+  return check_launch(c, "ln128_kernel");
+}
+
 template <int C>
 static int launch_ln_c(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, const float* g,
                        const float* b, float eps, int H, const float* pw, float* proj, long long plane,
@@ -178,7 +331,10 @@ int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy,
                    const bf16* msh, int mod_rows, cudaStream_t st, bf16* pbf, int tin, int tout, int tpitch) {
   if ((ldx & 3) || (ldy & 3)) return fail(c, XFOLD_ERR_ARG, "layernorm: row strides must be multiples of 4 elements");
   switch (C) {
-    case 128: return launch_ln_c<128>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
+    case 128:
+      if (((ldx | ldy) & 7) == 0)
+        return launch_ln128(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
+      return launch_ln_c<128>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
     case 384: return launch_ln_c<384>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
     case 768: return launch_ln_c<768>(c, x, ldx, y, ldy, rows, g, b, eps, H, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch, st);
   }

@@ -47,14 +47,11 @@ class DistributeGridSelfAttention(nn.Module):
             return triattn_update(pair, mask, self._packed, self.transpose)
         # row shard (starting node) / column shard (ending node) with the bias taken from the full pair
         fp = full_pair.to(torch.bfloat16).contiguous()
-        _, bias = ops.stage_triattn_bias(fp, self._packed, False)        # [4, N, N] key-major
+        _, bias_t = ops.stage_triattn_bias(fp, self._packed, False)      # [4, N, pad8(N)], [head, query, key]
         n = fp.shape[0]
-        ldq = (n + 7) // 8 * 8
-        bias_t = torch.zeros(4, n, ldq, dtype=torch.bfloat16, device=fp.device)
-        bias_t[..., :n] = bias
         z = pair.transpose(0, 1) if self.transpose else pair
         z = z.to(torch.bfloat16).contiguous()
-        x, _ = ops.stage_triattn_bias(z, self._packed, True)             # x = act_norm(shard)
+        x, _ = ops.stage_triattn_bias(z, self._packed, False)            # x = act_norm(shard)
         upd = torch.zeros_like(z)
         ops.stage_triattn_core(x, bias_t, mask, self._packed, upd)
         upd = upd.transpose(0, 1) if self.transpose else upd

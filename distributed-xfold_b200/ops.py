@@ -402,25 +402,25 @@ def stage_trimul_output(o: torch.Tensor, g: torch.Tensor, z: torch.Tensor, w: Pa
     check(rc, dev, "xfold_trimul_output_fwd")
 
 
-def stage_triattn_bias(z: torch.Tensor, w: PackedTriAttn, key_major_rows: bool):
-    """x = act_norm(z) and this shard's part of the key-major pair bias:
-    [4, N, R] when the rows are query rows, [4, R, pad8(N)] when they are key rows."""
+def stage_triattn_bias(z: torch.Tensor, w: PackedTriAttn, rows_are_keys: bool):
+    """x = act_norm(z) and this shard's part of the pair bias [head, query, key] (bf16):
+    [4, R, pad8(N)] when the shard's rows are query rows, [4, N, R] when they are key rows."""
     _need_cuda(z)
     dev = _dev(z)
     r, n, _ = z.shape
     x = torch.empty_like(z)
-    if key_major_rows:
-        pitch = _pad8(n)
-        bias = torch.zeros(4, r, pitch, dtype=BF16, device=z.device)
-        plane = r * pitch
-    else:
+    if rows_are_keys:
         pitch = _pad8(r)
         bias = torch.zeros(4, n, pitch, dtype=BF16, device=z.device)
         plane = n * pitch
+    else:
+        pitch = _pad8(n)
+        bias = torch.zeros(4, r, pitch, dtype=BF16, device=z.device)
+        plane = r * pitch
     rc = load().xfold_triattn_bias_fwd(ctx(dev), _ptr(z), r, n, C.byref(w.c), _ptr(x), _ptr(bias), pitch, plane,
-                                       int(key_major_rows), _stream(dev))
+                                       int(rows_are_keys), _stream(dev))
     check(rc, dev, "xfold_triattn_bias_fwd")
-    return x, (bias if key_major_rows else bias[..., :r])
+    return x, (bias[..., :r] if rows_are_keys else bias)
 
 
 def stage_triattn_core(x: torch.Tensor, bias_t: torch.Tensor, mask_shard: Optional[torch.Tensor], w: PackedTriAttn,
@@ -446,16 +446,16 @@ def stage_transition(x: torch.Tensor, w: PackedTransition) -> None:
 
 
 def stage_pair_logits(z: torch.Tensor, w: PackedPairformerBlock) -> torch.Tensor:
-    """Key-major pair logits contributed by this shard's (query) rows: bf16 [16, N, R]."""
+    """Pair logits [head, query, key] contributed by this shard's (query) rows: bf16 [16, R, pad8(N)]."""
     _need_cuda(z)
     dev = _dev(z)
     r, n, _ = z.shape
-    pitch = _pad8(r)
-    out = torch.zeros(16, n, pitch, dtype=BF16, device=z.device)
+    pitch = _pad8(n)
+    out = torch.zeros(16, r, pitch, dtype=BF16, device=z.device)
     rc = load().xfold_pair_logits_fwd(ctx(dev), _ptr(z), r, n, _ptr(w.spl_g), _ptr(w.spl_b), _ptr(w.spl_w), _ptr(out),
-                                      pitch, n * pitch, 0, _stream(dev))
+                                      pitch, r * pitch, 0, _stream(dev))
     check(rc, dev, "xfold_pair_logits_fwd")
-    return out[..., :r]
+    return out
 
 
 def stage_single_update(s: torch.Tensor, pl_t: torch.Tensor, seq_mask: Optional[torch.Tensor],

@@ -9,7 +9,7 @@ representation (zT[j][i] = z[i][j]):
 
     z   : TriMul outgoing        gather b rows            (all-gather, N*N*c / P elements per peer)
     zT  : TriMul incoming        gather b rows            'ckj,cki->cij' on z is 'cik,cjk->cij' on zT
-    z   : TriAttn starting node  gather the pair bias     (4 * N * N bf16 in total)
+    z   : TriAttn starting node  gather the pair bias     (4 * N * N bf16 in total, [head, query, key])
     zT  : TriAttn ending node    gather the pair bias, then pair Transition (token-local)
     z   : pair logits, gathered; the single path is replicated on every rank (it is < 1 % of the work)
 
@@ -123,20 +123,22 @@ def pairformer_block(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch
     o = stages.trimul_contract(a, sh.gather_rows(b), n)
     stages.trimul_output(o, g, zt, w.tri_in)
     del a, b, g, o
-    # TriangleAttention, starting node, on z: local rows are QUERY rows of the bias
+    # TriangleAttention, starting node, on z: the local rows are QUERY rows of the bias [head, query, key]
     z = sh.transpose(zt)
-    x, bias_loc = stages.triattn_bias(z, w.att_start, False)          # [4, N, R]
-    bias = sh.gather_last_dim(bias_loc, ldq)                          # [4, N, ldq]
+    x, bias_loc = stages.triattn_bias(z, w.att_start, False)          # [4, R, ldq]
+    bias = sh.gather_rows(bias_loc.transpose(0, 1).contiguous()).transpose(0, 1).contiguous()   # [4, N, ldq]
     stages.triattn_core(x, bias, pair_mask[rows], w.att_start, z)
-    # ending node on zT: local rows are KEY rows of the bias; mask rows as the reference passes them
+    # ending node on zT: token zT[j][i] is pair (i, j), so the local rows are KEY rows of the bias;
+    # the mask rows are the ones the reference passes (pair_mask[shard])
     zt = sh.transpose(z)
-    x, bias_loc = stages.triattn_bias(zt, w.att_end, True)            # [4, R, ldq]
-    bias = sh.gather_rows(bias_loc.transpose(0, 1).contiguous()).transpose(0, 1).contiguous()
+    x, bias_loc = stages.triattn_bias(zt, w.att_end, True)            # [4, N, R]
+    bias = sh.gather_last_dim(bias_loc, ldq)                          # [4, N, ldq]
     stages.triattn_core(x, bias, pair_mask[rows], w.att_end, zt)
     del x, bias, bias_loc
     stages.transition(zt, w.pair_transition)
     z = sh.transpose(zt)
     if s is not None and w.with_single:
-        pl_loc = stages.pair_logits(z, w)                             # [16, N, R]
-        stages.single_update(s, sh.gather_last_dim(pl_loc, ldq), seq_mask, w)
+        pl_loc = stages.pair_logits(z, w)                             # [16, R, ldq]
+        pl = sh.gather_rows(pl_loc.transpose(0, 1).contiguous()).transpose(0, 1).contiguous()
+        stages.single_update(s, pl, seq_mask, w)
     return z, s

@@ -210,22 +210,23 @@ int xfold_trimul_contract_fwd(xfold_ctx* ctx, const void* a, const void* b_full,
 /* z[R][N][128] += output_projection(center_norm(o)) * sigmoid(g)   (nn/d_triangle_multiplication.py:92-99) */
 int xfold_trimul_output_fwd(xfold_ctx* ctx, const void* o, int ldo, const void* g, int R, int N,
                             const xfold_trimul_weights* w, void* x_scratch, void* z, void* stream);
-/* x = act_norm(z) for R rows and the pair bias these rows contribute (nn/d_attention.py:61-62), bf16:
- * key_major_rows = 0: the rows are query rows x, biasT[h * plane + y * pitch + x_local];
- * key_major_rows = 1: the rows are key rows,     biasT[h * plane + row_local * pitch + y]. */
+/* x = act_norm(z) for R rows and the pair bias these rows contribute (nn/d_attention.py:61-62), bf16, laid out
+ * [head][query][key]:
+ * rows_are_keys = 0: the rows are query rows,  bias[h * plane + row_local * pitch + y];
+ * rows_are_keys = 1: the rows are key rows x,  bias[h * plane + y * pitch + x_local]. */
 int xfold_triattn_bias_fwd(xfold_ctx* ctx, const void* z, int R, int N, const xfold_triattn_weights* w, void* x,
-                           void* biasT, int pitch, long long plane, int key_major_rows, void* stream);
-/* z[R][N][128] += output_projection(gated attention(x)) along the second axis; biasT: bf16 [4][N][ldq], key-major,
- * gathered from all ranks; mask: float32, row b at mask + b * mask_ld. Scratch sizes from the function below. */
+                           void* bias, int pitch, long long plane, int rows_are_keys, void* stream);
+/* z[R][N][128] += output_projection(gated attention(x)) along the second axis; bias: bf16 [4][N][ldq],
+ * [head][query][key], gathered from all ranks; mask: float32, row b at mask + b * mask_ld. */
 size_t xfold_triattn_core_scratch_bytes(int R, int N, size_t* mext_bytes);
 int xfold_triattn_core_fwd(xfold_ctx* ctx, void* x, const void* biasT, int ldq, const float* mask, long long mask_ld,
                            int R, int N, const xfold_triattn_weights* w, void* qkvg_scratch, void* mext_scratch, void* z,
                            void* stream);
 /* Pair logits of the single path (nn/d_pairformer.py:158-160) for R rows, same layouts as the bias above (16 heads). */
 int xfold_pair_logits_fwd(xfold_ctx* ctx, const void* z, int R, int N, const float* ln_gamma, const float* ln_beta,
-                          const float* w16, void* plT, int pitch, long long plane, int key_major_rows, void* stream);
+                          const float* w16, void* plT, int pitch, long long plane, int rows_are_keys, void* stream);
 /* single += AttentionPairBias(single, plT) ; single += Transition(single)   (nn/d_pairformer.py:162-169);
- * plT: bf16 [16][N][ldq] key-major pair logits of the whole pair representation. */
+ * plT: bf16 [16][N][ldq] pair logits of the whole pair representation, [head][query][key]. */
 size_t xfold_single_update_workspace_bytes(int N);
 int xfold_single_update_fwd(xfold_ctx* ctx, void* s, const void* plT, int ldq, const float* seq_mask, int N,
                             const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);

@@ -42,24 +42,24 @@ class OracleStages:
         y = self.O.layer_norm(o.permute(0, 2, 1), st.get(p + "center_norm.weight"), st.get(p + "center_norm.bias"))
         z += F.linear(y, st[p + "output_projection.weight"]) * torch.sigmoid(g)
 
-    def triattn_bias(self, z, w, key_major_rows):
+    def triattn_bias(self, z, w, rows_are_keys):
         st, p = w
         x = self.O.layer_norm(z, st.get(p + "act_norm.weight"), st.get(p + "act_norm.bias"))
         nb = F.linear(x, st[p + "pair_bias_projection.weight"])     # [R, N, 4]
-        if key_major_rows:
-            out = torch.zeros(4, z.shape[0], _pad8(z.shape[1]))
-            out[..., : z.shape[1]] = nb.permute(2, 0, 1)
-            return x, out
-        return x, nb.permute(2, 1, 0).contiguous()                  # [4, N, R]
+        if rows_are_keys:
+            return x, nb.permute(2, 1, 0).contiguous()              # [4, N(query), R(key)]
+        out = torch.zeros(4, z.shape[0], _pad8(z.shape[1]))
+        out[..., : z.shape[1]] = nb.permute(2, 0, 1)                # [4, R(query), N(key)]
+        return x, out
 
-    def triattn_core(self, x, bias_t, mask_shard, w, z):
+    def triattn_core(self, x, bias, mask_shard, w, z):
         st, p = w
         r, n, c = x.shape
         h, d = 4, c // 4
         q = F.linear(x, st[p + "q_projection.weight"]).reshape(r, n, h, d).permute(0, 2, 1, 3) * d ** -0.5
         k = F.linear(x, st[p + "k_projection.weight"]).reshape(r, n, h, d).permute(0, 2, 1, 3)
         v = F.linear(x, st[p + "v_projection.weight"]).reshape(r, n, h, d).permute(0, 2, 1, 3)
-        logits = q @ k.transpose(-1, -2) + bias_t[:, :n, :n].transpose(1, 2)[None]
+        logits = q @ k.transpose(-1, -2) + bias[:, :n, :n][None]
         if mask_shard is not None:
             logits = logits + 1e9 * (mask_shard[:, None, None, :] - 1)
         o = (torch.softmax(logits, -1) @ v).permute(0, 2, 1, 3).reshape(r, n, c)
@@ -73,11 +73,12 @@ class OracleStages:
     def pair_logits(self, z, w):
         st, p = w.state, w.prefix
         x = self.O.layer_norm(z, st.get(p + "single_pair_logits_norm.weight"), st.get(p + "single_pair_logits_norm.bias"))
-        return F.linear(x, st[p + "single_pair_logits_projection.weight"]).permute(2, 1, 0).contiguous()  # [16, N, R]
+        out = torch.zeros(16, z.shape[0], _pad8(z.shape[1]))
+        out[..., : z.shape[1]] = F.linear(x, st[p + "single_pair_logits_projection.weight"]).permute(2, 0, 1)
+        return out                                                  # [16, R(query), pad8(N)(key)]
 
-    def single_update(self, s, pl_t, seq_mask, w):
+    def single_update(self, s, pl, seq_mask, w):
         st, p = w.state, w.prefix
         n = s.shape[0]
-        pl = pl_t[:, :n, :n].transpose(1, 2)
-        s += self.O.self_attention(st, p + "single_attention_.", s, seq_mask, pl, None, 16)
+        s += self.O.self_attention(st, p + "single_attention_.", s, seq_mask, pl[:, :n, :n], None, 16)
         s += self.O.transition(st, p + "single_transition.", s)
