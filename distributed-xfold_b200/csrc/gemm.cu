@@ -4,7 +4,8 @@
 //   warp 1      : tcgen05.mma issuer (one elected lane); owns the TMEM allocation (2 accumulators)
 //   warps 2..9  : epilogue; two warps share each 32-lane quarter of the 128-row accumulator (one per
 //                 half of the columns) and drain it with tcgen05.ld while the MMA warp already fills
-//                 the other buffer
+//                 the other buffer.  Row-major outputs leave through 128-byte-swizzled staging tiles
+//                 and TMA stores; residual and gate tiles of the 128-wide configuration come in by TMA.
 //
 // Every projection of the Pairformer block, the SwiGLU transition and the per-channel N x N x N
 // TriangleMultiplication contraction (batched over the 128 channels) run through this kernel; they
@@ -18,13 +19,20 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps
 
+constexpr uint32_t EPI_TILE = 128 * 64 * 2;  // one staged [128 rows][64 columns] bf16 chunk, 128-byte swizzled
+
 template <int BN>
 struct GemmCfg {
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = 4;
   static constexpr uint32_t A_BYTES = BM * BK * 2;
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  // after the operand ring: 2 output chunks; with 128-wide tiles also 2 residual and 2 gate chunks
+  static constexpr uint32_t OFF_OUT = STAGES * STAGE_BYTES;
+  static constexpr uint32_t OFF_RES = OFF_OUT + 2 * EPI_TILE;
+  static constexpr uint32_t OFF_GATE = OFF_RES + 2 * EPI_TILE;
+  static constexpr uint32_t OFF_BAR = (BN == 128) ? OFF_GATE + 2 * EPI_TILE : OFF_RES;
+  static constexpr uint32_t SMEM_BYTES = OFF_BAR + 256 /*barriers*/ + 1024 /*align slack*/;
 };
 
 __device__ __forceinline__ void store8_bf16(bf16* dst, const float* v, int nvalid, bool vec_ok) {
@@ -52,17 +60,23 @@ __device__ __forceinline__ void load8_bf16(const bf16* src, float* v, int nvalid
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmArgs p) {
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmO, const __grid_constant__ CUtensorMap tmR,
+               const __grid_constant__ CUtensorMap tmG, const GemmArgs p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::STAGES;
+  // residual / gate chunks are prefetched by TMA only in the 128-wide gate/residual configuration
+  constexpr bool EPI_LOADS = (EPI == EPI_GATE_RESID) && (BN == 128);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* efull = tempty + 2;   // [2] residual / gate chunk landed
+  uint64_t* eempty = efull + 2;   // [2] residual / gate chunk consumed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(eempty + 2);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -77,6 +91,8 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull[s], 1);
       mbar_init(&tempty[s], 8);
+      mbar_init(&efull[s], 1);
+      mbar_init(&eempty[s], 8);
     }
     *cta_abort = 0;
     fence_barrier_init();
@@ -97,8 +113,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, echunk = 0;
       bool okay = true;
+      (void)echunk;
       for (long long t = blockIdx.x; t < total && okay; t += gridDim.x) {
         const int tn = int(t % p.tiles_n);
         const int tm = int((t / p.tiles_n) % p.tiles_m);
@@ -107,6 +124,19 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (p.a_row_mode == 0) { a1 = tm * BM; a2 = b; }
         else { a1 = tm % p.a_dim1; a2 = (tm / p.a_dim1) * BM; }
         const int bb = p.b_batched ? b : 0;
+        if constexpr (EPI_LOADS) {
+          const uint32_t nload = (p.resid ? 1u : 0u) + (p.gate ? 1u : 0u);
+          if (nload) {
+            for (int c = 0; c < BN / 64 && okay; ++c, ++echunk) {
+              const uint32_t eb = echunk & 1u;
+              if (!mbar_wait(&eempty[eb], ((echunk >> 1) & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+              mbar_arrive_expect_tx(&efull[eb], nload * EPI_TILE);
+              if (p.resid) tma_load_3d(smem + Cfg::OFF_RES + eb * EPI_TILE, &tmR, &efull[eb], tn * BN + c * 64, tm * BM, 0);
+              if (p.gate) tma_load_3d(smem + Cfg::OFF_GATE + eb * EPI_TILE, &tmG, &efull[eb], tn * BN + c * 64, tm * BM, 0);
+            }
+            if (!okay) break;
+          }
+        }
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
@@ -146,7 +176,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int q = warp & 3;          // TMEM lane quarter this warp may read
     const int ch = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     const int row = q * 32 + lane;
-    uint32_t it = 0;
+    uint32_t it = 0, ochunk = 0, echunk = 0;
+    bool dead = false;
+    (void)ochunk; (void)echunk; (void)dead;
     for (long long t = blockIdx.x; t < total; t += gridDim.x, ++it) {
       const int tn = int(t % p.tiles_n);
       const int tm = int((t / p.tiles_n) % p.tiles_m);
@@ -156,80 +188,145 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(q * 32) << 16);
 
-      if constexpr (EPI == EPI_PLAIN || EPI == EPI_GATE_RESID) {
+      if constexpr (EPI != EPI_TRIMUL_AB) {
+        // Staged epilogue: the tile leaves in 64-column chunks.  Each of the 8 warps converts its 32 rows x 32
+        // columns of the chunk into a 128-byte-swizzled shared-memory tile (conflict-free 16-byte stores), then
+        // one thread hands the tile to TMA.  Residual / gate chunks arrive the same way in the other direction.
+        constexpr int NCH = (EPI == EPI_SWIGLU) ? BN / 128 : BN / 64;  // output chunks per tile
+        constexpr int WOUT = (EPI == EPI_SWIGLU) ? BN / 2 : BN;        // output columns per tile
+        const int n_out = (EPI == EPI_SWIGLU) ? p.N / 2 : p.N;
         const long long m = (long long)tm * BM + row;
-        const bool rvalid = m < p.M;
-        bf16* orow = p.out + (long long)b * p.out_batch_stride + m * p.ldo;
-        const bool vec_ok = ((p.ldo & 7) == 0);
+        const uint32_t rsw = uint32_t(row & 7);
+        const bool elected = (warp == 2 && lane == 0);
 #pragma unroll 1
-        for (int cc = ch * (BN / 64); cc < (ch + 1) * (BN / 64); ++cc) {
-          uint32_t r[32];
-          tmem_ld32(taddr + cc * 32, r);
-          tmem_ld_wait();
-          const int col0 = tn * BN + cc * 32;
-          if (rvalid && col0 < p.N) {
+        for (int c = 0; c < NCH; ++c, ++ochunk) {
+          const int col0 = tn * WOUT + c * 64;          // first output column of the chunk
+          const int colw = col0 + ch * 32;              // first output column of this warp
+          uint8_t* so = smem + Cfg::OFF_OUT + (ochunk & 1u) * EPI_TILE + row * 128;
+          float v[32];
+          if constexpr (EPI == EPI_SWIGLU) {
+            uint32_t ra[32], rb[32];
+            tmem_ld32(taddr + c * 64 + ch * 32, ra);
+            tmem_ld32(taddr + BN / 2 + c * 64 + ch * 32, rb);
+            tmem_ld_wait();
 #pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-              const int col = col0 + g8 * 8;
-              const int nvalid = p.N - col;
-              if (nvalid <= 0) break;
-              float v[8];
+            for (int e = 0; e < 32; ++e) {
+              const float x = __uint_as_float(ra[e]);
+              v[e] = x * sigmoidf_fast(x) * __uint_as_float(rb[e]);
+            }
+          } else {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 64 + ch * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[g8 * 8 + e]);
-              if constexpr (EPI == EPI_PLAIN) {
-                if (p.col_bias) {
+            for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
+          }
+          if constexpr (EPI == EPI_PLAIN) {
+            if (p.col_bias) {
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) v[e] += (e < nvalid) ? p.col_bias[col + e] : 0.f;
-                }
-                if (p.col_scale) {
+              for (int e = 0; e < 32; ++e) v[e] += (colw + e < n_out) ? p.col_bias[colw + e] : 0.f;
+            }
+            if (p.col_scale) {
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) v[e] *= (e < nvalid) ? p.col_scale[col + e] : 0.f;
-                }
-              } else {
-                if (p.gate) {
-                  float gv[8];
-                  load8_bf16(p.gate + m * p.ldg + col, gv, nvalid, (p.ldg & 7) == 0);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[e] *= sigmoidf_fast(gv[e]);
-                } else if (p.row_gate) {
-                  float gv[8];
-                  load8_bf16(p.row_gate + (m % p.row_gate_mod) * p.ldg + col, gv, nvalid, (p.ldg & 7) == 0);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[e] *= sigmoidf_fast(gv[e]);
-                }
-                if (p.resid) {
-                  float rv[8];
-                  load8_bf16(p.resid + m * p.ldr + col, rv, nvalid, (p.ldr & 7) == 0);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) v[e] += rv[e];
-                }
-              }
-              store8_bf16(orow + col, v, nvalid, vec_ok);
+              for (int e = 0; e < 32; ++e) v[e] *= (colw + e < n_out) ? p.col_scale[colw + e] : 0.f;
             }
           }
-        }
-      } else if constexpr (EPI == EPI_SWIGLU) {
-        // columns [0,128) of the tile are the SiLU half, [128,256) the linear half of the same outputs
-        const long long m = (long long)tm * BM + row;
-        const bool rvalid = m < p.M;
-        bf16* orow = p.out + m * p.ldo + tn * (BN / 2);
-#pragma unroll 1
-        for (int cc = ch * (BN / 128); cc < (ch + 1) * (BN / 128); ++cc) {
-          uint32_t ra[32], rb[32];
-          tmem_ld32(taddr + cc * 32, ra);
-          tmem_ld32(taddr + BN / 2 + cc * 32, rb);
-          tmem_ld_wait();
-          if (rvalid) {
-#pragma unroll
-            for (int g8 = 0; g8 < 4; ++g8) {
-              float v[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                const float a = __uint_as_float(ra[g8 * 8 + e]);
-                v[e] = a * sigmoidf_fast(a) * __uint_as_float(rb[g8 * 8 + e]);
+          if constexpr (EPI == EPI_GATE_RESID) {
+            // order: v * sigmoid(gate) first, residual added last
+            const bool rvalid = m < p.M;
+            bool staged = false;
+            uint32_t eb = 0;
+            if constexpr (EPI_LOADS) {
+              if (p.resid || p.gate) {
+                staged = true;
+                eb = echunk & 1u;
+                if (!mbar_wait(&efull[eb], (echunk >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) dead = true;
+                ++echunk;
               }
-              store8_bf16(orow + cc * 32 + g8 * 8, v, 8, true);
             }
+            if (p.gate) {
+              if (staged) {
+                const uint8_t* sg = smem + Cfg::OFF_GATE + eb * EPI_TILE + row * 128;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint4 u = *reinterpret_cast<const uint4*>(sg + ((uint32_t(ch * 4 + g) ^ rsw) << 4));
+                  const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    v[g * 8 + 2 * e] *= sigmoidf_fast(bf16_lo(w4[e]));
+                    v[g * 8 + 2 * e + 1] *= sigmoidf_fast(bf16_hi(w4[e]));
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const int col = colw + g * 8, nvalid = rvalid ? n_out - col : 0;
+                  if (nvalid <= 0) continue;
+                  float t8[8];
+                  load8_bf16(p.gate + m * p.ldg + col, t8, nvalid, (p.ldg & 7) == 0);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[g * 8 + e] *= sigmoidf_fast(t8[e]);
+                }
+              }
+            }
+            if (p.row_gate) {  // gate shared by rows with equal (row % mod): AdaLN-Zero conditioning of several samples
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const int col = colw + g * 8, nvalid = rvalid ? n_out - col : 0;
+                if (nvalid <= 0) continue;
+                float t8[8];
+                load8_bf16(p.row_gate + (m % p.row_gate_mod) * p.ldg + col, t8, nvalid, (p.ldg & 7) == 0);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[g * 8 + e] *= sigmoidf_fast(t8[e]);
+              }
+            }
+            if (p.resid) {
+              if (staged) {
+                const uint8_t* sr = smem + Cfg::OFF_RES + eb * EPI_TILE + row * 128;
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint4 u = *reinterpret_cast<const uint4*>(sr + ((uint32_t(ch * 4 + g) ^ rsw) << 4));
+                  const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    v[g * 8 + 2 * e] += bf16_lo(w4[e]);
+                    v[g * 8 + 2 * e + 1] += bf16_hi(w4[e]);
+                  }
+                }
+              } else {
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const int col = colw + g * 8, nvalid = rvalid ? n_out - col : 0;
+                  if (nvalid <= 0) continue;
+                  float t8[8];
+                  load8_bf16(p.resid + m * p.ldr + col, t8, nvalid, (p.ldr & 7) == 0);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) v[g * 8 + e] += t8[e];
+                }
+              }
+            }
+            if (staged) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&eempty[eb]);
+            }
+          }
+          // the TMA store that last used this staging buffer (two chunks ago) must have read it out
+          if (elected) tma_store_wait_read<1>();
+          named_bar_sync(1, 256);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+            u.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+            u.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+            u.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(so + ((uint32_t(ch * 4 + g) ^ rsw) << 4)) = u;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(2, 256);
+          if (elected && col0 < n_out) {
+            tma_store_3d(&tmO, smem + Cfg::OFF_OUT + (ochunk & 1u) * EPI_TILE, col0, tm * BM, b);
+            tma_store_commit();
           }
         }
       } else {  // EPI_TRIMUL_AB
@@ -287,6 +384,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[buf]);
     }
+    if (warp == 2 && lane == 0) tma_store_wait_read<0>();  // staged tiles must be read out before the CTA exits
   }
 
   tc_fence_before();
@@ -315,13 +413,26 @@ static int launch_one(Ctx* c, const CUtensorMap& tmA, const CUtensorMap& tmB, co
   }
   const long long total = (long long)a.batches * a.tiles_m * a.tiles_n;
   if (total <= 0) return XFOLD_OK;
+  CUtensorMap tmO = tmA, tmR = tmA, tmG = tmA;  // placeholders when unused
+  if (EPI != EPI_TRIMUL_AB) {
+    const int n_out = (EPI == EPI_SWIGLU) ? a.N / 2 : a.N;
+    const uint64_t bstride = a.batches > 1 ? (uint64_t)a.out_batch_stride : (uint64_t)a.ldo * (uint64_t)a.M;
+    if (!make_tmap_bf16_3d(&tmO, a.out, n_out, a.M, a.batches, a.ldo, bstride, 64, 128, 1))
+      return fail(c, XFOLD_ERR_ARG, "gemm: cannot encode the output tensor map (16-byte aligned base, ld multiple of 8?)");
+    if (EPI == EPI_GATE_RESID && BN == 128) {
+      if (a.resid && !make_tmap_bf16_3d(&tmR, a.resid, a.N, a.M, 1, a.ldr, (uint64_t)a.ldr * a.M, 64, 128, 1))
+        return fail(c, XFOLD_ERR_ARG, "gemm: cannot encode the residual tensor map");
+      if (a.gate && !make_tmap_bf16_3d(&tmG, a.gate, a.N, a.M, 1, a.ldg, (uint64_t)a.ldg * a.M, 64, 128, 1))
+        return fail(c, XFOLD_ERR_ARG, "gemm: cannot encode the gate tensor map");
+    }
+  }
   const int grid = (int)(total < c->sm_count ? total : c->sm_count);
   const int tag = EPI == EPI_TRIMUL_AB ? XFOLD_K_TRIMUL_PROJ
                   : EPI == EPI_SWIGLU  ? XFOLD_K_LINEAR_SWIGLU
                   : EPI == EPI_GATE_RESID ? XFOLD_K_LINEAR_GATE_RESID
                   : (a.batches > 1 ? XFOLD_K_TRIMUL_CONTRACT : XFOLD_K_LINEAR);
   ProfScope ps(c, tag, st);
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, a);
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, st>>>(tmA, tmB, tmO, tmR, tmG, a);
   return check_launch(c, "gemm_tn_kernel");
 }
 

@@ -169,7 +169,11 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
   constexpr int SLOTS = (H == 0) ? 4 : (H == 4 ? 2 : 1);
   extern __shared__ float s_pw[];  // H x 128 projection weights
   if constexpr (H > 0) {
-    for (int i = threadIdx.x; i < H * 128; i += blockDim.x) s_pw[i] = pw[i];
+    // stored as [head][half][lane16][4] so that the 16 lanes of a row read consecutive 16-byte words
+    for (int i = threadIdx.x; i < H * 128; i += blockDim.x) {
+      const int h = i >> 7, c = i & 127;
+      s_pw[((h * 2 + ((c >> 2) & 1)) * 16 + (c >> 3)) * 4 + (c & 3)] = pw[i];
+    }
     __syncthreads();
   }
   const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
@@ -245,8 +249,8 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
           float acc[G];
 #pragma unroll
           for (int h = 0; h < G; ++h) {
-            const float4 w0 = *reinterpret_cast<const float4*>(s_pw + (hb + h) * 128 + c0);
-            const float4 w1 = *reinterpret_cast<const float4*>(s_pw + (hb + h) * 128 + c0 + 4);
+            const float4 w0 = *reinterpret_cast<const float4*>(s_pw + (((hb + h) * 2 + 0) * 16 + l16) * 4);
+            const float4 w1 = *reinterpret_cast<const float4*>(s_pw + (((hb + h) * 2 + 1) * 16 + l16) * 4);
             acc[h] = v[0] * w0.x + v[1] * w0.y + v[2] * w0.z + v[3] * w0.w + v[4] * w1.x + v[5] * w1.y + v[6] * w1.z +
                      v[7] * w1.w;
           }
@@ -348,7 +352,7 @@ int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy,
 // ---------------------------------------------------------------------------------------------
 constexpr int CMLN_TOK = 128;
 constexpr int CMLN_PITCH = CMLN_TOK + 8;  // elements; keeps every row 16-byte aligned
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, long long row_stride, int R, int N,
              bf16* __restrict__ out, const float* __restrict__ gamma, const float* __restrict__ beta, float eps) {
   __shared__ __align__(16) bf16 tile[128][CMLN_PITCH];
