@@ -27,7 +27,7 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as ge  # noqa: E402
 
 KERNEL_CLASSES = ["layernorm", "trimul_proj", "trimul_contract", "channel_ln", "linear_gate_resid", "linear",
-                  "attention", "linear_swiglu", "mask_bias", "swiglu"]
+                  "attention", "linear_swiglu", "mask_bias", "swiglu", "peer_exchange"]
 
 
 def flops_block(n, c=128, cs=384):

@@ -33,6 +33,9 @@ def run_multi(args, world, rank, local_rank):
     z_h, s_h, pm_h, sm_h = O.make_inputs(3, n, pad_frac=0.1)
     sh = row_sharded.RowSharding(n)
     stages = row_sharded.CudaStages()
+    peer = sh.enable_peer_exchange(dev) and os.environ.get("XFOLD_NO_PEER") != "1"
+    if not peer:
+        sh.peer = None
     z_h = z_h[sh.rows].to(torch.bfloat16).contiguous().pin_memory()
     s_h = s_h.to(torch.bfloat16).pin_memory()
     z_out_h, s_out_h = torch.empty_like(z_h).pin_memory(), torch.empty_like(s_h).pin_memory()
@@ -121,7 +124,7 @@ def run_multi(args, world, rank, local_rank):
                 "e2e": {"value": ms_e2e, "unit": "ms", "h2d_bytes_per_step": (z_h.numel() + s_h.numel()) * 2 * world,
                         "d2h_bytes_per_step": (z_h.numel() + s_h.numel()) * 2 * world},
                 "roofline": roof, "model_tflops": flops_block(n) * nb / (ms_step * 1e-3) / 1e12,
-                "rank0_kernel_ms_per_step": kern_ms, "rank0_exchange_and_glue_ms_per_step": ms_step - kern_ms,
+                "rank0_kernel_ms_per_step": kern_ms, "rank0_exchange_and_glue_ms_per_step": ms_step - kern_ms, "peer_memory_transpose": bool(peer),
                 "kernels": per_kernel}
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -76,6 +76,8 @@ SIGNATURES = {
     "xfold_triangle_multiplication_update_fwd": (ci, [vp, vp, vp, vp, ci, ci, C.POINTER(TriMulWeights), vp, sz, vp]),
     "xfold_triangle_attention_update_fwd": (ci, [vp, vp, vp, vp, ci, ci, C.POINTER(TriAttnWeights), vp, sz, vp]),
     "xfold_transition_update_fwd": (ci, [vp, vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp, sz, vp]),
+    "xfold_transpose_scatter_fwd": (ci, [vp, vp, ci, ci, ci, C.POINTER(vp), C.POINTER(ci), ci, vp]),
+    "xfold_peer_barrier": (ci, [vp, C.POINTER(vp), ci, ci, ci, vp]),
     "xfold_transition_static_max_bytes": (sz, []),
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),
     "xfold_pairformer_workspace_bytes": (sz, [ci]),

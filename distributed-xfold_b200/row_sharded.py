@@ -85,15 +85,74 @@ class RowSharding:
         out[..., : self.n] = parts.movedim(0, -1)
         return out
 
+    def enable_peer_exchange(self, device) -> bool:
+        """Switches ``transpose`` to the one-kernel peer-memory exchange over NVLink (symmetric-memory
+        buffers mapped into every rank + the C-ABI scatter / flag-barrier kernels).  Returns False, and keeps
+        the send/recv path, when symmetric memory cannot be set up."""
+        if self.world == 1:
+            return False
+        try:
+            self.peer = PeerExchange(self, device)
+            return True
+        except Exception as e:  # pragma: no cover - depends on the machine's P2P capabilities
+            self.peer = None
+            self.peer_error = repr(e)
+            return False
+
     def transpose(self, z: torch.Tensor) -> torch.Tensor:
         """Row shard of z [R_me, N, c] -> row shard of z^T: out[j_local, i] = z_global[i, j_global]."""
         if self.world == 1:
             return z.transpose(0, 1).contiguous()
+        if getattr(self, "peer", None) is not None and z.is_cuda:
+            return self.peer.transpose(z)
         c = z.shape[-1]
         send = [z[:, sl, :].transpose(0, 1).contiguous() for sl in self.slices]          # to q: [R_q, R_me, c]
         recv = [z.new_empty((self.r, sz, c)) for sz in self.sizes]                       # from p: [R_me, R_p, c]
         _exchange(send, recv, self.group)
         return torch.cat(recv, dim=1)
+
+
+class PeerExchange:
+    """Distributed transpose through peer-mapped memory: each rank stores its tokens directly into the
+    owning rank's buffer with one kernel (``xfold_transpose_scatter_fwd``), then the ranks meet at a bounded
+    flag barrier (``xfold_peer_barrier``).  Two buffers alternate, so a buffer is rewritten only after the
+    barrier that follows its last read (see the ordering argument in the module docstring of the C source)."""
+
+    def __init__(self, sh: "RowSharding", device, channels: int = 128):
+        import torch.distributed._symmetric_memory as symm
+        from . import peer_ops as ops
+        self.sh, self.ops, self.c = sh, ops, channels
+        group = sh.group if sh.group is not None else dist.group.WORLD
+        rmax = max(sh.sizes)
+        self.bufs, self.ptrs = [], []
+        for _ in range(2):
+            t = symm.empty(rmax * sh.n * channels, dtype=torch.bfloat16, device=device)
+            h = symm.rendezvous(t, group)
+            off = t.data_ptr() - int(h.buffer_ptrs[sh.rank])
+            self.bufs.append(t)
+            self.ptrs.append([int(p) + off for p in h.buffer_ptrs])
+        self.flags = symm.empty(8, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        h = symm.rendezvous(self.flags, group)
+        off = self.flags.data_ptr() - int(h.buffer_ptrs[sh.rank])
+        self.flag_ptrs = [int(p) + off for p in h.buffer_ptrs]
+        self.starts = [sl.start for sl in sh.slices] + [sh.n]
+        self.k = 0
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=sh.group)  # every rank's flags are zero before anyone signals
+
+    def transpose(self, z: torch.Tensor) -> torch.Tensor:
+        sh = self.sh
+        z = z.contiguous()
+        k = self.k
+        if z.data_ptr() == self.bufs[k].data_ptr():  # never scatter a buffer into itself
+            k ^= 1
+        self.ops.transpose_scatter(z, sh.rows.start, self.ptrs[k], self.starts)
+        self.epoch += 1
+        self.ops.peer_barrier(self.flag_ptrs, sh.rank, sh.world, self.epoch, z.device)
+        self.k = k ^ 1
+        return self.bufs[k][: sh.r * sh.n * self.c].view(sh.r, sh.n, self.c)
 
 
 class CudaStages:

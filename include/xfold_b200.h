@@ -58,7 +58,8 @@ enum {
   XFOLD_K_LINEAR_SWIGLU = 7,
   XFOLD_K_MASK_BIAS = 8,
   XFOLD_K_SWIGLU = 9,
-  XFOLD_K_COUNT = 10
+  XFOLD_K_PEER = 10,
+  XFOLD_K_COUNT = 11
 };
 long long xfold_launch_count(xfold_ctx* ctx);
 int xfold_profile_enable(xfold_ctx* ctx, int on);
@@ -230,6 +231,22 @@ int xfold_pair_logits_fwd(xfold_ctx* ctx, const void* z, int R, int N, const flo
 size_t xfold_single_update_workspace_bytes(int N);
 int xfold_single_update_fwd(xfold_ctx* ctx, void* s, const void* plT, int ldq, const float* seq_mask, int N,
                             const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
+
+/* ---- peer-memory exchange (multi-GPU) ------------------------------------------------------------
+ * Replaces the reference's all-gather + re-slice of the whole pair representation between the
+ * row-sharded and column-sharded halves of a block (nn/d_pairformer.py:134-156) by a distributed
+ * transpose done in ONE kernel per rank: every token z[i][j][0..127] of this rank's R rows (global row
+ * row0 + i) is stored into the buffer of the rank that owns column j, at zT[j - col_starts[q]][row0 + i][:].
+ * peer_bufs: host array of `world` device pointers (each rank's destination buffer, mapped into this
+ * process, e.g. CUDA IPC / symmetric memory); col_starts: host array of world + 1 column offsets
+ * (ShardInfo rule, distribute_utils.py:101-128).  Plain stores over NVLink, no multicast. */
+int xfold_transpose_scatter_fwd(xfold_ctx* ctx, const void* z, int R, int N, int row0, void* const* peer_bufs,
+                                const int* col_starts, int world, void* stream);
+/* Flag barrier between the ranks (the reference uses dist.barrier, run_inference.py:154-245): rank `me`
+ * stores `epoch` into slot `me` of every rank's flag array (peer_flags[q], 8 ints, zero-initialised) and
+ * waits until all slots of its own array reached `epoch`.  The wait is bounded; a time-out is reported by
+ * xfold_check_status as XFOLD_ERR_TIMEOUT.  Epochs must increase by one per call. */
+int xfold_peer_barrier(xfold_ctx* ctx, void* const* peer_flags, int me, int world, int epoch, void* stream);
 
 /* ---- update-only variants ----------------------------------------------------------------------
  * The reference's module forwards return the update and the caller adds it (`pair += module(pair, ...)`,
