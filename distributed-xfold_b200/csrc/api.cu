@@ -108,7 +108,7 @@ static int gemm_rows(Ctx* c, int epi, const bf16* x, long long ldx, long long M,
 }
 
 static int linear_plain(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N, const float* bias,
-                        const float* scale, bf16* out, long long ldo, cudaStream_t st) {
+                        const float* scale, bf16* out, long long ldo, cudaStream_t st, int f16_col0 = 0, int f16_col1 = 0) {
   if (M >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "linear: too many rows");
   GemmArgs a;
   const int bn = (N > 128) ? 256 : 128;
@@ -118,6 +118,8 @@ static int linear_plain(Ctx* c, const bf16* x, long long ldx, long long M, int K
   a.ldo = ldo;
   a.col_bias = bias;
   a.col_scale = scale;
+  a.f16_col0 = f16_col0;
+  a.f16_col1 = f16_col1;
   return gemm_rows(c, EPI_PLAIN, x, ldx, M, K, w, N, K, a, bn, st);
 }
 
@@ -325,7 +327,8 @@ static int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float
                         int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st,
                         bf16* upd = nullptr) {
   const long long M = (long long)R * N;
-  int rc = linear_plain(c, x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, qkvg, 512, st);
+  // the v columns are stored as fp16: the attention kernel's P V product runs with fp16 operands
+  int rc = linear_plain(c, x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, qkvg, 512, st, 256, 384);
   if (rc) return rc;
   if ((rc = launch_mext(c, mask, mask_ld, mext, R, N, st))) return rc;
   const long long seq_stride = transposed ? (long long)R * 128 : 128;
@@ -395,7 +398,8 @@ static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int 
   apb_ws(B, S, H, Dp, &cv, &W);
   if (!ws || !cv.ok()) return fail(c, XFOLD_ERR_ARG, "apb: workspace too small (%zu < %zu)", ws_bytes, cv.off);
   const int Wd = H * Dp;
-  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, W.qkvg, 4 * Wd, st);
+  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, W.qkvg, 4 * Wd, st,
+                        Dp == 32 ? 2 * Wd : 0, Dp == 32 ? 3 * Wd : 0);
   if (rc) return rc;
   if (Dp == 32) {
     if (!pair_biasT) {

@@ -28,6 +28,8 @@
 // threads are bank-conflict free.
 #include <cstdlib>
 
+#include <cuda_fp16.h>
+
 #include "internal.h"
 #include "umma.cuh"
 
@@ -194,7 +196,8 @@ attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUt
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(128, 128);
-      constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1);
+      constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
+                                                                  // projection buffer are written as fp16 by the GEMM
       const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
       const uint64_t mxd = make_sdesc_noswizzle(smem_u32(sMext), 128, 256);
       const long long my_items = n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
@@ -327,25 +330,33 @@ attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUt
           }
         }
         if (!mbar_wait(&turn[w], g & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
+        // Exponentials two at a time: the exponents are packed to fp16x2 (x <= 8, so 2^x <= 256 fits; the fp16
+        // spacing of x costs < 0.5 % relative error in P for every term that matters), one ex2.approx.f16x2
+        // serves two keys, and P goes to shared memory as fp16 for the P V product.  Row sums accumulate in four
+        // fp16x2 registers (16 terms each, <= 4096) and are combined in fp32.
+        __half2 hs[4] = {__float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f)};
+#pragma unroll
+        for (int c8 = 0; c8 < 16; ++c8) {  // 8 keys -> one 16-byte store
+          uint32_t pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float x0 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e]), LOG2E, -m_ref);
+            const float x1 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e + 1]), LOG2E, -m_ref);
+            const __half2 xh = __floats2half2_rn(x0, x1);
+            uint32_t ph;
+            asm("ex2.approx.f16x2 %0, %1;" : "=r"(ph) : "r"(*reinterpret_cast<const uint32_t*>(&xh)));
+            hs[e] = __hadd2(hs[e], *reinterpret_cast<const __half2*>(&ph));
+            pk[e] = ph;
+          }
+          *reinterpret_cast<uint4*>(myP + (c8 >> 3) * A2_T + ((uint32_t(c8 & 7) ^ rsw) << 4)) =
+              make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
         float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const float p0 = ex2f_(fmaf(__uint_as_float(r[cc * 32 + 2 * e]), LOG2E, -m_ref));
-            const float p1 = ex2f_(fmaf(__uint_as_float(r[cc * 32 + 2 * e + 1]), LOG2E, -m_ref));
-            ls0 += p0;
-            ls1 += p1;
-            pk[e] = pack_bf16x2(p0, p1);
-          }
-          uint8_t* prow = myP + (cc >> 1) * A2_T;
-#pragma unroll
-          for (int gg = 0; gg < 4; ++gg) {
-            const uint32_t chunk = uint32_t((cc & 1) * 4 + gg) ^ rsw;
-            *reinterpret_cast<uint4*>(prow + chunk * 16) =
-                make_uint4(pk[4 * gg], pk[4 * gg + 1], pk[4 * gg + 2], pk[4 * gg + 3]);
-          }
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(hs[e]);
+          ls0 += f.x;
+          ls1 += f.y;
         }
         l_run += ls0 + ls1;
         mbar_arrive(&turn[w ^ 1]);
@@ -410,7 +421,10 @@ __global__ void mext_kernel(const float* __restrict__ mask, long long mask_ld, b
     const long long bb = tile / KB;
     const int k = kb * 128 + r;
     float v = -1.0e30f;
-    if (k < S) v = mask ? 1.0e9f * (mask[bb * mask_ld + k] - 1.f) : 0.f;
+    // 1e9 * (mask - 1) as in the reference, floored at -60000: any such logit still exponentiates to exactly 0
+    // next to an unmasked one, while a row whose keys are ALL masked keeps fp32-resolvable logits (at 1e9 the
+    // fp32 spacing is 64, which would turn into exponents of +-128 and overflow the fp16 exponentials)
+    if (k < S) v = mask ? fmaxf(1.0e9f * (mask[bb * mask_ld + k] - 1.f), -60000.f) : 0.f;
     uint4 lo = make_uint4(uint32_t(__bfloat16_as_ushort(__float2bfloat16(v))), 0, 0, 0);
     uint8_t* t = reinterpret_cast<uint8_t*>(out) + tile * 4096 + (r >> 3) * 256 + (r & 7) * 16;
     *reinterpret_cast<uint4*>(t) = lo;

@@ -10,10 +10,17 @@
 // Every projection of the Pairformer block, the SwiGLU transition and the per-channel N x N x N
 // TriangleMultiplication contraction (batched over the 128 channels) run through this kernel; they
 // differ only in the tensor maps and in the epilogue that is fused behind the accumulator.
+#include <cuda_fp16.h>
+
 #include "internal.h"
 #include "umma.cuh"
 
 namespace xf {
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -313,13 +320,22 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           // the TMA store that last used this staging buffer (two chunks ago) must have read it out
           if (elected) tma_store_wait_read<1>();
           named_bar_sync(1, 256);
+          bool as_f16 = false;
+          if constexpr (EPI == EPI_PLAIN) as_f16 = colw >= p.f16_col0 && colw < p.f16_col1;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 u;
-            u.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
-            u.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
-            u.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
-            u.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+            if (as_f16) {
+              u.x = pack_f16x2(v[g * 8 + 0], v[g * 8 + 1]);
+              u.y = pack_f16x2(v[g * 8 + 2], v[g * 8 + 3]);
+              u.z = pack_f16x2(v[g * 8 + 4], v[g * 8 + 5]);
+              u.w = pack_f16x2(v[g * 8 + 6], v[g * 8 + 7]);
+            } else {
+              u.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+              u.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+              u.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+              u.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+            }
             *reinterpret_cast<uint4*>(so + ((uint32_t(ch * 4 + g) ^ rsw) << 4)) = u;
           }
           fence_proxy_async_smem();

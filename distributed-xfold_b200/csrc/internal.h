@@ -78,6 +78,7 @@ struct GemmArgs {
   long long ldo = 0, out_batch_stride = 0;
   const float* col_bias = nullptr;
   const float* col_scale = nullptr;
+  int f16_col0 = 0, f16_col1 = 0;  // PLAIN: output columns [f16_col0, f16_col1) are stored as fp16 (multiples of 32)
   const bf16* resid = nullptr;
   long long ldr = 0;
   const bf16* gate = nullptr;

@@ -167,10 +167,11 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 }
 
 // Instruction descriptor: bf16 x bf16 -> fp32, M x N tile; a_mn / b_mn = 1 for an MN-major operand.
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn = 0, int b_mn = 0) {
-  return (1u << 4)               // D format fp32
-         | (1u << 7)             // A format bf16
-         | (1u << 10)            // B format bf16
+// ab_f16 = 1: both operands are fp16 instead of bf16 (the two must have the same type for kind::f16).
+__host__ __device__ constexpr uint32_t make_idesc(int M, int N, int a_mn = 0, int b_mn = 0, int ab_f16 = 0) {
+  return (1u << 4)                          // D format fp32
+         | ((ab_f16 ? 0u : 1u) << 7)        // A format: bf16 (1) or fp16 (0)
+         | ((ab_f16 ? 0u : 1u) << 10)       // B format
          | (uint32_t(a_mn) << 15) | (uint32_t(b_mn) << 16)
          | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
