@@ -2,29 +2,34 @@
 // 24-wide heads padded to 32): the softmax warps never touch global memory.
 //
 // Work item = 128 queries of one batch row x 2 heads (one head per softmax warpgroup); CTAs are persistent
-// (one per SM) and pipeline consecutive items into each other.
-//   warp 0      : TMA producer.  Q once; per 128-key block: K tile (+ the 4 KB mask-bias tile),
-//                 one bf16 pair-bias tile per head, V tile.  Every buffer is single: a tile is
-//                 re-filled as soon as the MMAs that read it have committed, which is long before
-//                 it is needed again.
-//   warp 1      : tcgen05.mma issuer.  A softmax thread pulls its whole 128-wide logits row out of TMEM in
-//                 one go, so the logits of block n+1 are produced while block n is being exponentiated;
-//                 O accumulates in TMEM across key blocks and is rescaled lazily (only when a row maximum
-//                 grows by more than 2^8).  For each head the logits accumulator is built from two
-//                 products:  S  = Q K^T                      (K = 32)
-//                            S += E1 * Mext^T                (K = 16; column 0 of E1 is all ones,
-//                                                             column 0 of Mext is the additive
-//                                                             mask bias of each key)
-//                 then O += P V once the warpgroup has published P.  (tcgen05.mma costs ~65-85 cycles per
-//                 instruction whatever its N, so the issuing thread is kept to 11 instructions per head
-//                 and key block; adding the pair bias with an identity-matrix product, tried first, made
-//                 that thread the bottleneck.)
-//   warps 2..5 / 6..9 : softmax warpgroups, one thread per query row: pair bias added from the shared-memory
-//                 tile, row max, ex2, row sum, P as bf16 into a swizzled K-major tile; running offset / sum in
-//                 registers, output in TMEM.
+// (one per SM) and run their items' 64-key blocks as one continuous, double-buffered sequence.
+//   warp 0      : TMA producer.  Q per item; per 64-key block the K tile (+ the 2 KB mask-bias tile) and the V
+//                 tile; two stages each.
+//   warps 1, 10 : tcgen05.mma issuers, one per warpgroup, so that the two heads never wait for each other.
+//                 Per block:  S  = Q K^T                      (K = 32, N = 64)
+//                             S += E1 * Mext^T                (K = 16; column 0 of E1 is all ones, column 0
+//                                                              of Mext is the additive mask bias of each key)
+//                             O += P V                        (K = 64, N = 32; O stays in TMEM for the item)
+//                 S and P are double-buffered: S(n+2) is issued when the warpgroup publishes P(n), so logits
+//                 are always waiting when a softmax pass starts.  The issuer also fetches its warpgroup's
+//                 bf16 pair-bias tile two blocks ahead.
+//   warps 2..5 / 6..9 : softmax warpgroups, one thread per query row.
+//
+// The exponential unit (16 lanes per SM) is the bound of this kernel: 2 x 128 x 64 exponentials per block are
+// 2 x 512 cycles of it, and measurements show that it only overlaps with the other pipes when ONE warp's
+// instruction stream interleaves both kinds of work -- a warp that takes maxima while another one
+// exponentiates does not overlap with it.  The softmax pass is therefore a single sweep per block that
+// exponentiates against the running reference exponent m_ref of the PREVIOUS blocks,
+//     x = s * log2(e) + bias * log2(e) - m_ref  (fp32)  ->  fp16x2  ->  running max (fp16x2), ex2.approx.f16x2,
+//     row sum (fp16x2 partial sums), P as fp16 into a swizzled K-major tile,
+// and only looks at the block maximum afterwards: if some row of the warp saw x > 8 (P > 256; fp16 would
+// overflow beyond 2^16), the warp takes the exact path -- fp32 row maximum from the logits still held in
+// registers, O (TMEM) and the row sum rescaled, the sweep repeated.  The first block of an item always takes
+// the exact path.  With trained or random weights the repeat is rare after the first block, so the common
+// block costs one sweep.
 //
 // The pair bias arrives as bf16 [head][query][key] (key contiguous, row pitch a multiple of 8); TMA lays a
-// [128 queries][64 keys] half tile out with the 128-byte swizzle, so the per-row 16-byte reads of the softmax
+// [128 queries][64 keys] tile out with the 128-byte swizzle, so the per-row 16-byte reads of the softmax
 // threads are bank-conflict free.
 #include <cstdlib>
 
@@ -49,12 +54,17 @@ struct Attn2Args {
   int* status;
 };
 
-constexpr int A2_THREADS = 320;
-constexpr uint32_t A2_T = 16384;  // [128][64] bf16 tile
-// Q, K, V, bias[2][2], P[2][2] tiles, then E1 and Mext (4 KB each), then barriers
-constexpr uint32_t A2_OFF_Q = 0, A2_OFF_K = A2_T, A2_OFF_V = 2 * A2_T, A2_OFF_BIAS = 3 * A2_T, A2_OFF_P = 7 * A2_T,
-                   A2_OFF_E1 = 11 * A2_T, A2_OFF_MEXT = 11 * A2_T + 4096, A2_OFF_BAR = 11 * A2_T + 8192;
-constexpr uint32_t A2_SMEM = A2_OFF_BAR + 256 + 1024;
+constexpr int A2_THREADS = 352;   // TMA warp, 2 MMA warps, 2 x 4 softmax warps
+constexpr uint32_t A2_T = 16384;  // [128][64] 2-byte tile
+constexpr uint32_t A2_H = 8192;   // [64][64] 2-byte tile
+constexpr int A2_KV = 4;           // K / V stages: their rows come from DRAM (~1.3 us under load), three blocks of lead
+// Q[2], K[4], V[4], bias[2 warpgroups][2], E1, Mext[4], barriers
+constexpr uint32_t A2_OFF_Q = 0, A2_OFF_K = 2 * A2_T, A2_OFF_V = 4 * A2_T, A2_OFF_BIAS = 6 * A2_T,
+                   A2_OFF_E1 = 10 * A2_T, A2_OFF_MEXT = 10 * A2_T + 4096, A2_OFF_BAR = 10 * A2_T + 4096 + 8192;
+// TMEM columns: logits S of warpgroup w, buffer s at w*128 + s*64 (64 columns); output O of warpgroup w at
+// 256 + w*32; probabilities P of warpgroup w, buffer s at 320 + w*64 + s*32 (64 keys as 32 fp16 pairs).
+constexpr uint32_t A2_TM_O = 256, A2_TM_P = 320;
+constexpr uint32_t A2_SMEM = A2_OFF_BAR + 512 + 1024;
 
 __device__ __forceinline__ float ex2f_(float x) {
   float y;
@@ -75,70 +85,82 @@ __device__ __forceinline__ void tmem_st32_(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+#ifdef A2_TIMELINE
+__device__ long long* g_a2_tl = nullptr;
+#define TL(role, ev) do { if (blockIdx.x == 0 && tl && tln < 4000) tl[(role) * 4096 + tln++] = (clock64() << 8) | (ev); } while (0)
+#else
+#define TL(role, ev) do {} while (0)
+#endif
+
 __global__ void __launch_bounds__(A2_THREADS, 1)
-attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUtensorMap tmb, const Attn2Args p) {
+attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmkv,
+             const __grid_constant__ CUtensorMap tmb, const Attn2Args p) {
   constexpr int D = 32;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint8_t* sQ = smem + A2_OFF_Q;
-  uint8_t* sK = smem + A2_OFF_K;
-  uint8_t* sV = smem + A2_OFF_V;
-  uint8_t* sBias = smem + A2_OFF_BIAS;  // warpgroup w: 2 tiles [128 queries][keys 0..63 | 64..127]
-  uint8_t* sP = smem + A2_OFF_P;        // warpgroup w: 2 tiles (keys 0..63, 64..127)
+  uint8_t* sQ = smem + A2_OFF_Q;        // [item & 1]
+  uint8_t* sK = smem + A2_OFF_K;        // [block & 3], 8 KB each
+  uint8_t* sV = smem + A2_OFF_V;        // [block & 3], 8 KB each
+  uint8_t* sBias = smem + A2_OFF_BIAS;  // [warpgroup][block & 1]: [128 queries][64 keys] bf16
   uint8_t* sE1 = smem + A2_OFF_E1;
-  uint8_t* sMext = smem + A2_OFF_MEXT;
+  uint8_t* sMext = smem + A2_OFF_MEXT;  // [block & 3], 2 KB each
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A2_OFF_BAR);
-  uint64_t* q_full = bars;
-  uint64_t* q_empty = bars + 1;
-  uint64_t* k_full = bars + 2;
-  uint64_t* k_empty = bars + 3;
-  uint64_t* v_full = bars + 4;
-  uint64_t* v_empty = bars + 5;
-  uint64_t* bias_full = bars + 6;   // [2]
-  uint64_t* bias_empty = bars + 8;  // [2]
-  uint64_t* s_full = bars + 10;     // [2] logits of a block are in TMEM
-  uint64_t* pv_done = bars + 12;    // [2] P V product of a block complete
-  uint64_t* p_ready = bars + 14;    // [2] P of a block is in shared memory
-  uint64_t* s_read = bars + 16;     // [2] logits of a block are in registers
-  uint64_t* turn = bars + 18;       // [2] warpgroup w may run its exponential phase
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
+  uint64_t* q_full = bars;            // [2]
+  uint64_t* q_empty = bars + 2;       // [2] both issuers have committed the item's last logits
+  uint64_t* k_full = bars + 4;        // [4]
+  uint64_t* k_empty = bars + 8;       // [4] both issuers have committed the block's logits
+  uint64_t* v_full = bars + 12;       // [4]
+  uint64_t* v_empty = bars + 16;      // [4] both issuers have committed the block's P V product
+  uint64_t* sb_full = bars + 20;      // [warpgroup][2] logits of a block are in TMEM and its bias tile has landed
+  uint64_t* pv_done = bars + 24;      // [warpgroup][2] P V product of a block complete
+  uint64_t* p_ready = bars + 28;      // [warpgroup][2] P of a block is in TMEM (and its logits, bias consumed).  One
+                                      // barrier per buffer: a warp may finish block g + 1 (its logits are waiting)
+                                      // before a slower warp of the warpgroup has finished block g, and its arrival
+                                      // must not be counted for block g.
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef A2_TIMELINE
+  long long* tl = (lane == 0) ? g_a2_tl : nullptr;
+  int tln = 0;
+#endif
   const AbortCtx ab{cta_abort, p.status};
-  const int KB = (p.S + 127) / 128;
+  const int KB = (p.S + 63) / 64;
   // Persistent CTA: work items (batch row, head pair, query tile), batch row slowest so that the K / V rows of
-  // the ~gridDim.x items in flight stay in L2; every role walks the same item sequence and all barriers keep
-  // counting across items, so the next item's loads and first logits overlap the current item's tail.
+  // the ~gridDim.x items in flight stay in L2.  Every role walks the same sequence of blocks; block numbers
+  // (and with them buffer indices and barrier phases) keep counting across items.
   const int QT = (p.S + 127) / 128, HP = p.heads / 2;
   const long long n_items = (long long)p.B * HP * QT;
-  auto decode = [&](long long t, int& qt, int& hp, int& b) {
-    qt = int(t % QT);
-    hp = int((t / QT) % HP);
-    b = int(t / ((long long)QT * HP));
+  const uint32_t my_items = n_items > blockIdx.x ? uint32_t((n_items - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
+  const uint32_t G = my_items * uint32_t(KB);  // blocks this CTA processes in total (the launcher bounds items * KB to 2^31)
+  auto decode = [&](uint32_t it, int& qt, int& hp, int& b) {
+    const uint32_t t = blockIdx.x + it * gridDim.x;
+    qt = int(t % uint32_t(QT));
+    hp = int((t / uint32_t(QT)) % uint32_t(HP));
+    b = int(t / uint32_t(QT * HP));
   };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    mbar_init(k_full, 1);
-    mbar_init(k_empty, 1);
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&bias_full[s], 1);
-      mbar_init(&bias_empty[s], 128);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&pv_done[s], 1);
+      mbar_init(&q_full[s], 1);
+      mbar_init(&q_empty[s], 2);
+    }
+    for (int s = 0; s < 4; ++s) {
       mbar_init(&p_ready[s], 128);
-      mbar_init(&s_read[s], 128);
-      mbar_init(&turn[s], 128);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 2);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 2);
+      mbar_init(&sb_full[s], 2);  // the issuer's expect-tx arrival for the bias tile + the commit of the logits
+      mbar_init(&pv_done[s], 1);
     }
     *cta_abort = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&tm);
+    tma_prefetch_desc(&tmq);
+    tma_prefetch_desc(&tmkv);
     tma_prefetch_desc(&tmb);
   }
   // constant operand E1: un-swizzled [128][16] tile whose column 0 is all ones
@@ -160,96 +182,100 @@ attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUt
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;        // items started by this CTA
-      uint32_t g = 0;         // key blocks started by this CTA (all items)
+      uint32_t j = 0;  // block number
       bool okay = true;
-      for (long long t = blockIdx.x; t < n_items && okay; t += gridDim.x, ++it) {
+      for (uint32_t it = 0; it < my_items && okay; ++it) {
         int qt, hp, b;
-        decode(t, qt, hp, b);
-        auto load = [&](uint8_t* dst, uint64_t* bar, int col, int seq0) {
-          if (p.transposed) tma_load_3d(dst, &tm, bar, col, b, seq0);
-          else tma_load_3d(dst, &tm, bar, col, seq0, b);
-        };
-        if (!mbar_wait(q_empty, (it & 1) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(q_full, A2_T);
-        load(sQ, q_full, p.q_col0 + hp * 64, qt * 128);
+        decode(it, qt, hp, b);
+        const uint32_t qs = uint32_t(it & 1), qpar = uint32_t((it >> 1) & 1);
+        if (!mbar_wait(&q_empty[qs], qpar ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(&q_full[qs], A2_T);
+        if (p.transposed) tma_load_3d(sQ + qs * A2_T, &tmq, &q_full[qs], p.q_col0 + hp * 64, b, qt * 128);
+        else tma_load_3d(sQ + qs * A2_T, &tmq, &q_full[qs], p.q_col0 + hp * 64, qt * 128, b);
         const bf16* mrow = p.mext + (long long)b * p.mext_batch_stride;
-        for (int kb = 0; kb < KB && okay; ++kb, ++g) {
-          const uint32_t par = (g & 1) ^ 1u;
-          if (!mbar_wait(k_empty, par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-          mbar_arrive_expect_tx(k_full, A2_T + 4096);
-          load(sK, k_full, p.k_col0 + hp * 64, kb * 128);
-          bulk_load(sMext, mrow + (long long)kb * 2048, 4096, k_full);
-          for (int w = 0; w < 2 && okay; ++w) {
-            if (!mbar_wait(&bias_empty[w], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-            mbar_arrive_expect_tx(&bias_full[w], 2 * A2_T);
-            tma_load_3d(sBias + w * 2 * A2_T, &tmb, &bias_full[w], kb * 128, qt * 128, hp * 2 + w);
-            tma_load_3d(sBias + w * 2 * A2_T + A2_T, &tmb, &bias_full[w], kb * 128 + 64, qt * 128, hp * 2 + w);
-          }
-          if (!okay) break;
-          if (!mbar_wait(v_empty, par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-          mbar_arrive_expect_tx(v_full, A2_T);
-          load(sV, v_full, p.v_col0 + hp * 64, kb * 128);
+        for (int kb = 0; kb < KB; ++kb, ++j) {
+          const uint32_t st = uint32_t(j & (A2_KV - 1)), par = uint32_t((j / A2_KV) & 1) ^ 1u;
+          if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          TL(0, 1);
+          mbar_arrive_expect_tx(&k_full[st], A2_H + 2048);
+          if (p.transposed) tma_load_3d(sK + st * A2_H, &tmkv, &k_full[st], p.k_col0 + hp * 64, b, kb * 64);
+          else tma_load_3d(sK + st * A2_H, &tmkv, &k_full[st], p.k_col0 + hp * 64, kb * 64, b);
+          bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
+          if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          TL(0, 4);
+          mbar_arrive_expect_tx(&v_full[st], A2_H);
+          if (p.transposed) tma_load_3d(sV + st * A2_H, &tmkv, &v_full[st], p.v_col0 + hp * 64, b, kb * 64);
+          else tma_load_3d(sV + st * A2_H, &tmkv, &v_full[st], p.v_col0 + hp * 64, kb * 64, b);
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 10) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(128, 128);
+      const int w = warp == 1 ? 0 : 1;
+      constexpr uint32_t idesc_s = make_idesc(128, 64);
       constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
                                                                   // projection buffer are written as fp16 by the GEMM
       const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
-      const uint64_t mxd = make_sdesc_noswizzle(smem_u32(sMext), 128, 256);
-      const long long my_items = n_items > blockIdx.x ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-      const long long G = my_items * KB;  // key blocks this CTA processes in total
-      // TMEM per warpgroup w: logits S at columns w*128 .. +127, output accumulator O at 256 + w*32 .. +31.
-      // A softmax thread pulls its whole logits row into registers at once, so S(g+1) is issued as soon as that
-      // load has finished (s_read), i.e. while block g is still being exponentiated -- across item boundaries too.
-      auto issue_s = [&](long long g, int w) -> bool {
-        const int kb = int(g % KB);
-        const uint32_t it = uint32_t(g / KB);
-        if (w == 0 && kb == 0 && !mbar_wait(q_full, it & 1, ab, XF_ERR_WAIT_FULL)) return false;
-        if (w == 0 && !mbar_wait(k_full, g & 1, ab, XF_ERR_WAIT_FULL)) return false;
+      // The block whose logits and bias tile are issued next (two blocks ahead of the P V products), tracked
+      // incrementally: this thread's instruction stream is the pacemaker of its warpgroup, so it carries no
+      // divisions and probes the K / V barriers before it parks on p_ready.
+      uint32_t aj = 0, ait = 0;
+      int akb = 0, aqt, ahp, ab_;
+      decode(0, aqt, ahp, ab_);
+      auto issue_ahead = [&](bool k_ready) -> bool {
+        const uint32_t s = aj & 1u, ks = aj & uint32_t(A2_KV - 1), kpar = (aj / A2_KV) & 1u;
+        if (akb == 0 && !mbar_wait(&q_full[ait & 1], (ait >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+        if (!k_ready && !mbar_wait(&k_full[ks], kpar, ab, XF_ERR_WAIT_FULL)) return false;
+        if (w == 0) TL(1, 17);
         tc_fence_after();
-        const uint32_t d = tmem_base + w * 128;
-        const uint64_t qd = make_sdesc(smem_u32(sQ) + w * 64, 16, 1024);
-        const uint64_t kd = make_sdesc(smem_u32(sK) + w * 64, 16, 1024);
+        const uint32_t d = tmem_base + w * 128 + s * 64;
+        const uint64_t qd = make_sdesc(smem_u32(sQ) + (ait & 1u) * A2_T + w * 64, 16, 1024);
+        const uint64_t kd = make_sdesc(smem_u32(sK) + ks * A2_H + w * 64, 16, 1024);
+        const uint64_t mxd = make_sdesc_noswizzle(smem_u32(sMext) + ks * 2048, 128, 256);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) umma_ss(d, qd + 2 * k, kd + 2 * k, idesc_s, k ? 1u : 0u);
         umma_ss(d, e1d, mxd, idesc_s, 1u);
-        umma_commit(&s_full[w]);
-        if (w == 1) {
-          umma_commit(k_empty);
-          if (kb == KB - 1) umma_commit(q_empty);  // last use of this item's Q tile
+        umma_commit(&sb_full[w * 2 + s]);
+        umma_commit(&k_empty[ks]);
+        if (akb == KB - 1) umma_commit(&q_empty[ait & 1]);  // last use of this item's Q tile
+        mbar_arrive_expect_tx(&sb_full[w * 2 + s], A2_T);
+        tma_load_3d(sBias + (w * 2 + s) * A2_T, &tmb, &sb_full[w * 2 + s], akb * 64, aqt * 128, ahp * 2 + w);
+        ++aj;
+        if (++akb == KB) {
+          akb = 0;
+          ++ait;
+          decode(ait, aqt, ahp, ab_);
         }
         return true;
       };
-      bool okay = G > 0;
-      for (int w = 0; w < 2 && okay; ++w) okay = issue_s(0, w);
-      for (long long g = 0; g < G && okay; ++g) {
-        if (g + 1 < G) {
-          for (int w = 0; w < 2 && okay; ++w) {
-            if (!mbar_wait(&s_read[w], g & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
-            okay = issue_s(g + 1, w);
-          }
-        }
-        const int kb = int(g % KB);
-        for (int w = 0; w < 2 && okay; ++w) {
-          if (!mbar_wait(&p_ready[w], g & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
-          if (w == 0 && !mbar_wait(v_full, g & 1, ab, XF_ERR_WAIT_FULL)) { okay = false; break; }
-          tc_fence_after();
-          const uint32_t pbase = smem_u32(sP + w * 2 * A2_T);
-          const uint32_t vbase = smem_u32(sV) + w * 64;
-          const uint32_t d = tmem_base + 256 + w * 32;
+      bool okay = true;
+      while (aj < 2 && aj < G && okay) okay = issue_ahead(false);
+      int kb = 0;  // key block of block g within its item
+      for (uint32_t g = 0; g < G && okay; ++g) {
+        const uint32_t s = g & 1u, vs = g & uint32_t(A2_KV - 1), vpar = (g / A2_KV) & 1u;
+        // K and V tiles are fetched blocks ahead: probe their barriers now, so that the round trips overlap the wait below
+        const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
+        const bool k_ready = aj < G && mbar_test_wait(&k_full[aj & uint32_t(A2_KV - 1)], (aj / A2_KV) & 1u);
+        if (!mbar_wait(&p_ready[w * 2 + s], (g >> 1) & 1u, ab, XF_ERR_WAIT_ATTN)) break;
+        if (w == 0) TL(1, 14);
+        // P(g) is published (and with it the logits buffer and bias tile of block g are free for block g + 2)
+        if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
+        if (w == 0) TL(1, 15);
+        tc_fence_after();
+        const uint32_t pt = tmem_base + A2_TM_P + w * 64 + s * 32;
+        const uint32_t vbase = smem_u32(sV) + vs * A2_H + w * 64;
+        const uint32_t d = tmem_base + A2_TM_O + w * 32;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t ad = make_sdesc(pbase + (ks >> 2) * A2_T + (ks & 3) * 32, 16, 1024);
-            const uint64_t bd = make_sdesc(vbase + ks * 2048, A2_T, 1024);  // V is N-major: 16 keys = 2048 B
-            umma_ss(d, ad, bd, idesc_pv, (kb | ks) ? 1u : 0u);              // O accumulates across the item's key blocks
-          }
-          umma_commit(&pv_done[w]);
-          if (w == 1) umma_commit(v_empty);
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t bd = make_sdesc(vbase + ks * 2048, A2_T, 1024);  // V is N-major: 16 keys = 2048 B
+          umma_ts(d, pt + ks * 8, bd, idesc_pv, (kb | ks) ? 1u : 0u);     // 16 keys = 8 columns of P; O accumulates
         }
+        umma_commit(&pv_done[w * 2 + s]);
+        umma_commit(&v_empty[vs]);
+        if (++kb == KB) kb = 0;
+        if (w == 0) TL(1, 16);
+        if (aj < G) okay = issue_ahead(k_ready);
+        if (w == 0) TL(1, 18);
       }
     }
   } else {
@@ -258,99 +284,107 @@ attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUt
     const int row = q4 * 32 + lane;
     const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
     const uint32_t s_addr = tmem_base + w * 128 + lane_addr;
-    const uint32_t o_addr = tmem_base + 256 + w * 32 + lane_addr;
-    uint8_t* myP = sP + w * 2 * A2_T + row * 128;
-    const uint8_t* myBias = sBias + w * 2 * A2_T + row * 128;
+    const uint32_t o_addr = tmem_base + A2_TM_O + w * 32 + lane_addr;
+    const uint32_t p_addr = tmem_base + A2_TM_P + w * 64 + lane_addr;
     const uint32_t rsw = uint32_t(row & 7);
-    uint32_t g = 0;  // key blocks processed by this CTA so far
+#ifdef A2_TIMELINE
+    if (q4 != 2) tl = nullptr;
+#endif
+    uint32_t g = 0;  // block number
     bool okay = true;
-    // The two warpgroups share each scheduler's exponential unit (one warp of each per scheduler).  They take
-    // turns in the ex2-heavy phase, so that one adds bias / takes maxima on the ALU while the other
-    // exponentiates, instead of both queueing on the same unit at the same time.  Warpgroup 0 starts.
-    if (w == 1) mbar_arrive(&turn[0]);
-    for (long long t = blockIdx.x; t < n_items && okay; t += gridDim.x) {
+    bool ready = false;  // the probe of this block's barrier, made before the previous block's sweep, succeeded
+    for (uint32_t it = 0; it < my_items && okay; ++it) {
       int qt, hp, b;
-      decode(t, qt, hp, b);
+      decode(it, qt, hp, b);
       const int qi = qt * 128 + row;
       const bool qvalid = qi < p.S;
-      // m_ref is the exponent offset in use (log2 units).  It follows the running maximum lazily: the output
-      // accumulator in TMEM is rescaled only when some row of the warp saw its maximum grow by more than 2^8,
-      // so most key blocks skip the TMEM round trip; until then P values up to 256 are harmless in bf16 / fp32.
+      // m_ref: exponent offset in use (log2 units); it follows the running maximum lazily (see the file header).
       float m_ref = -3.0e38f, l_run = 0.f;
       for (int kb = 0; kb < KB; ++kb, ++g) {
-        if (!mbar_wait(&s_full[w], g & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
+        const uint32_t s = uint32_t(g & 1), par = uint32_t((g >> 1) & 1);
+        const uint8_t* myBias = sBias + (w * 2 + s) * A2_T + row * 128;
+        // One barrier covers the logits and the bias tile.  It also covers the P buffer: the issuer queued
+        // S(g) behind the P V product of block g - 2, so P buffer s has been consumed when S(g) is complete.
+        if (!ready && !mbar_wait(&sb_full[w * 2 + s], par, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
+        TL(2 + w, 20);
         tc_fence_after();
-        uint32_t r[128];
-        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
-        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-        tmem_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(&r[64]));
-        tmem_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(&r[96]));
+        uint32_t r[64];
+        tmem_ld32(s_addr + s * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(s_addr + s * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        ready = mbar_test_wait(&sb_full[w * 2 + (s ^ 1u)], uint32_t(((g + 1) >> 1) & 1));  // probe block g + 1
         tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(&s_read[w]);  // the logits are in registers: the buffer may take the next block
-        // add the pair bias (bf16 tile [128 queries][128 keys] in two swizzled halves, this thread's row) and
-        // take the row maximum in the same pass
-        if (!mbar_wait(&bias_full[w], g & 1, ab, XF_ERR_WAIT_FULL)) { okay = false; break; }
-        float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
+        TL(2 + w, 22);
+        bool exact = kb == 0;
+        __half2 hs[4];
+        uint32_t pk[32];
+        for (;;) {
+          if (exact) {
+            // fp32 row maximum of this block; move the reference if it grew by more than 2^8
+            float mx0 = -3.0e38f, mx1 = -3.0e38f, mx2 = -3.0e38f, mx3 = -3.0e38f;
 #pragma unroll
-        for (int c8 = 0; c8 < 16; ++c8) {
-          const uint4 bq = *reinterpret_cast<const uint4*>(myBias + (c8 >> 3) * A2_T + ((uint32_t(c8 & 7) ^ rsw) << 4));
-          const int e = c8 * 8;
-          float t;
-          t = __uint_as_float(r[e + 0]) + bf16_lo(bq.x); r[e + 0] = __float_as_uint(t); mx0 = fmaxf(mx0, t);
-          t = __uint_as_float(r[e + 1]) + bf16_hi(bq.x); r[e + 1] = __float_as_uint(t); mx1 = fmaxf(mx1, t);
-          t = __uint_as_float(r[e + 2]) + bf16_lo(bq.y); r[e + 2] = __float_as_uint(t); mx2 = fmaxf(mx2, t);
-          t = __uint_as_float(r[e + 3]) + bf16_hi(bq.y); r[e + 3] = __float_as_uint(t); mx3 = fmaxf(mx3, t);
-          t = __uint_as_float(r[e + 4]) + bf16_lo(bq.z); r[e + 4] = __float_as_uint(t); mx0 = fmaxf(mx0, t);
-          t = __uint_as_float(r[e + 5]) + bf16_hi(bq.z); r[e + 5] = __float_as_uint(t); mx1 = fmaxf(mx1, t);
-          t = __uint_as_float(r[e + 6]) + bf16_lo(bq.w); r[e + 6] = __float_as_uint(t); mx2 = fmaxf(mx2, t);
-          t = __uint_as_float(r[e + 7]) + bf16_hi(bq.w); r[e + 7] = __float_as_uint(t); mx3 = fmaxf(mx3, t);
-        }
-        mbar_arrive(&bias_empty[w]);  // the bias tile may be refilled for the next block
-        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * LOG2E;
-        // the previous P V product must be complete before P (shared memory) or O (TMEM) are touched
-        if (kb > 0) {
-          if (!mbar_wait(&pv_done[w], (g - 1) & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
-          tc_fence_after();
-        }
-        const bool grow = mx > m_ref + 8.f;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float m_new = grow ? mx : m_ref;
-          const float alpha = ex2f_(m_ref - m_new);
-          m_ref = m_new;
-          l_run *= alpha;
-          if (kb > 0) {
-            uint32_t o[32];
-            tmem_ld32(o_addr, o);
-            tmem_ld_wait();
+            for (int c8 = 0; c8 < 8; ++c8) {
+              const uint4 bq = *reinterpret_cast<const uint4*>(myBias + ((uint32_t(c8) ^ rsw) << 4));
+              const int e = c8 * 8;
+              mx0 = fmaxf(mx0, __uint_as_float(r[e + 0]) + bf16_lo(bq.x));
+              mx1 = fmaxf(mx1, __uint_as_float(r[e + 1]) + bf16_hi(bq.x));
+              mx2 = fmaxf(mx2, __uint_as_float(r[e + 2]) + bf16_lo(bq.y));
+              mx3 = fmaxf(mx3, __uint_as_float(r[e + 3]) + bf16_hi(bq.y));
+              mx0 = fmaxf(mx0, __uint_as_float(r[e + 4]) + bf16_lo(bq.z));
+              mx1 = fmaxf(mx1, __uint_as_float(r[e + 5]) + bf16_hi(bq.z));
+              mx2 = fmaxf(mx2, __uint_as_float(r[e + 6]) + bf16_lo(bq.w));
+              mx3 = fmaxf(mx3, __uint_as_float(r[e + 7]) + bf16_hi(bq.w));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * LOG2E;
+            const bool grow = mx > m_ref + 8.f;
+            if (__any_sync(0xffffffffu, grow)) {
+              const float m_new = grow ? mx : m_ref;
+              const float alpha = ex2f_(m_ref - m_new);
+              m_ref = m_new;
+              l_run *= alpha;
+              if (kb > 0) {
+                // every earlier P V product of the item must have landed before O is rescaled
+                const uint32_t gp = g - 1;
+                if (!mbar_wait(&pv_done[w * 2 + (gp & 1)], uint32_t((gp >> 1) & 1), ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
+                tc_fence_after();
+                uint32_t o[32];
+                tmem_ld32(o_addr, o);
+                tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st32_(o_addr, o);
-            tmem_st_wait_();
+                for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                tmem_st32_(o_addr, o);
+                tmem_st_wait_();
+              }
+            }
           }
-        }
-        if (!mbar_wait(&turn[w], g & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
-        // Exponentials two at a time: the exponents are packed to fp16x2 (x <= 8, so 2^x <= 256 fits; the fp16
-        // spacing of x costs < 0.5 % relative error in P for every term that matters), one ex2.approx.f16x2
-        // serves two keys, and P goes to shared memory as fp16 for the P V product.  Row sums accumulate in four
-        // fp16x2 registers (16 terms each, <= 4096) and are combined in fp32.
-        __half2 hs[4] = {__float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f), __float2half2_rn(0.f)};
+          // the sweep: exponent, fp16x2 pack, running max, exponential, row sum, P store (8 keys per 16-byte store)
+          const float nm = -m_ref;
+          __half2 hm = __float2half2_rn(-65504.f);
 #pragma unroll
-        for (int c8 = 0; c8 < 16; ++c8) {  // 8 keys -> one 16-byte store
-          uint32_t pk[4];
+          for (int e = 0; e < 4; ++e) hs[e] = __float2half2_rn(0.f);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float x0 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e]), LOG2E, -m_ref);
-            const float x1 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e + 1]), LOG2E, -m_ref);
-            const __half2 xh = __floats2half2_rn(x0, x1);
-            uint32_t ph;
-            asm("ex2.approx.f16x2 %0, %1;" : "=r"(ph) : "r"(*reinterpret_cast<const uint32_t*>(&xh)));
-            hs[e] = __hadd2(hs[e], *reinterpret_cast<const __half2*>(&ph));
-            pk[e] = ph;
+          for (int c8 = 0; c8 < 8; ++c8) {
+            const uint4 bq = *reinterpret_cast<const uint4*>(myBias + ((uint32_t(c8) ^ rsw) << 4));
+            const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x0 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e]), LOG2E, nm);
+              float x1 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e + 1]), LOG2E, nm);
+              x0 = fmaf(bf16_lo(bw[e]), LOG2E, x0);
+              x1 = fmaf(bf16_hi(bw[e]), LOG2E, x1);
+              const __half2 xh = __floats2half2_rn(x0, x1);
+              hm = __hmax2(hm, xh);
+              uint32_t ph;
+              asm("ex2.approx.f16x2 %0, %1;" : "=r"(ph) : "r"(*reinterpret_cast<const uint32_t*>(&xh)));
+              hs[e] = __hadd2(hs[e], *reinterpret_cast<const __half2*>(&ph));
+              pk[c8 * 4 + e] = ph;
+            }
           }
-          *reinterpret_cast<uint4*>(myP + (c8 >> 3) * A2_T + ((uint32_t(c8 & 7) ^ rsw) << 4)) =
-              make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          if (exact) break;
+          const float2 bm = __half22float2(hm);
+          if (!__any_sync(0xffffffffu, fmaxf(bm.x, bm.y) > 8.f)) break;
+          exact = true;  // some row outgrew the reference: exact maximum, rescale, sweep again
         }
+        if (!okay) break;
         float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -359,14 +393,18 @@ attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUt
           ls1 += f.y;
         }
         l_run += ls0 + ls1;
-        mbar_arrive(&turn[w ^ 1]);
+        tmem_st32_(p_addr + s * 32, pk);
+        tmem_st_wait_();
+        TL(2 + w, 27);
         tc_fence_before();
-        fence_proxy_async_smem();
-        mbar_arrive(&p_ready[w]);
+        mbar_arrive(&p_ready[w * 2 + s]);
       }
       if (!okay || KB == 0) break;
-      // item epilogue: O / l, gate, store.  The next item's first logits are already being produced.
-      if (!mbar_wait(&pv_done[w], (g - 1) & 1, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
+      // item epilogue: O / l, gate, store (the next item's logits are already waiting)
+      {
+        const uint32_t gp = g - 1;
+        if (!mbar_wait(&pv_done[w * 2 + (gp & 1)], uint32_t((gp >> 1) & 1), ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
+      }
       tc_fence_after();
       uint32_t o[32];
       tmem_ld32(o_addr, o);
@@ -391,12 +429,14 @@ attn2_kernel(const __grid_constant__ CUtensorMap tm, const __grid_constant__ CUt
           *reinterpret_cast<uint4*>(orow + g8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
       }
+      TL(2 + w, 28);
     }
   }
 
   tc_fence_before();
   __syncthreads();
   if (*cta_abort && threadIdx.x == 0) {
+    // an aborted wait may have left copies in flight: give them time to land before the CTA's memory is released
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000) {}
   }
@@ -472,21 +512,23 @@ int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int tra
                       bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st) {
   if ((width & 7) || (ldq & 7) || (heads & 1)) return fail(c, XFOLD_ERR_ARG, "attention: width and bias pitch must be multiples of 8, heads even");
   if (S <= 0 || B <= 0) return XFOLD_OK;
-  CUtensorMap tm, tmb;
+  CUtensorMap tmq, tmkv, tmb;
   bool ok;
   Attn2Args a;
   if (!transposed) {
-    ok = make_tmap_bf16_3d(&tm, qkvg, width, S, B, width, (uint64_t)width * S, 64, 128, 1);
+    ok = make_tmap_bf16_3d(&tmq, qkvg, width, S, B, width, (uint64_t)width * S, 64, 128, 1) &&
+         make_tmap_bf16_3d(&tmkv, qkvg, width, S, B, width, (uint64_t)width * S, 64, 64, 1);
     a.seq_stride = width;
     a.batch_stride = (long long)S * width;
   } else {
-    ok = make_tmap_bf16_3d(&tm, qkvg, width, B, S, width, (uint64_t)width * B, 64, 1, 128);
+    ok = make_tmap_bf16_3d(&tmq, qkvg, width, B, S, width, (uint64_t)width * B, 64, 1, 128) &&
+         make_tmap_bf16_3d(&tmkv, qkvg, width, B, S, width, (uint64_t)width * B, 64, 1, 64);
     a.seq_stride = (long long)B * width;
     a.batch_stride = width;
   }
   ok = ok && make_tmap_bf16_3d(&tmb, biasT, S, S, heads, ldq, (uint64_t)ldq * S, 64, 128, 1);  // dims: key, query, head
   if (!ok) return fail(c, XFOLD_ERR_ARG, "attention: cannot encode tensor maps");
-  const int KB = (S + 127) / 128;
+  const int KB = (S + 127) / 128;  // 128-key mask tiles (two 64-key blocks each)
   a.S = S;
   a.B = B;
   a.q_col0 = q_col0;
@@ -509,9 +551,16 @@ int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int tra
     attr_done[c->device & 7] = true;
   }
   const long long items = (long long)((S + 127) / 128) * (heads / 2) * B;
+  if (items * ((S + 63) / 64) >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "attention: batch x heads x sequence too large for one launch");
   const int grid = (int)(items < c->sm_count ? items : c->sm_count);
+#ifdef A2_TIMELINE
+  if (const char* e = getenv("XFOLD_ATTN_TL")) {
+    long long* ptr = (long long*)strtoull(e, nullptr, 16);
+    cudaMemcpyToSymbol(g_a2_tl, &ptr, sizeof(ptr));
+  }
+#endif
   ProfScope ps(c, XFOLD_K_ATTENTION, st);
-  attn2_kernel<<<grid, A2_THREADS, A2_SMEM, st>>>(tm, tmb, a);
+  attn2_kernel<<<grid, A2_THREADS, A2_SMEM, st>>>(tmq, tmkv, tmb, a);
   return check_launch(c, "attn2_kernel");
 }
 

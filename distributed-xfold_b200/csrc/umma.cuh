@@ -61,26 +61,53 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a phase (a test that succeeds has acquire semantics like a wait).  A barrier round trip
+// costs ~250 cycles on this part, so a consumer probes the NEXT tile's barrier before it starts on the
+// current tile and only falls back to the blocking wait when the probe failed.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Shared by every role of a CTA: [0] = abort flag.
 struct AbortCtx {
   volatile int* cta_abort;  // shared memory
   int* status;              // global memory
 };
 
+// Blocking form with a suspend-time hint: the hardware parks the thread until the phase completes or the hint
+// (nanoseconds) runs out, instead of having it poll.  A polling loop of even one thread per warp takes issue
+// slots from the warps that do the arithmetic on the same scheduler.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. Returns false when the CTA is aborting.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*ab.cta_abort) return false;
   const long long t0 = clock64();
-  uint32_t it = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if (((++it) & 63u) == 0u) {
-      if (*ab.cta_abort) return false;
-      if (clock64() - t0 > XF_WAIT_CYCLES) {
-        *ab.cta_abort = 1;
-        atomicCAS(ab.status, 0, code);
-        return false;
-      }
+  while (!mbar_try_wait_parked(bar, parity, 20000u)) {
+    if (*ab.cta_abort) return false;
+    if (clock64() - t0 > XF_WAIT_CYCLES) {
+      *ab.cta_abort = 1;
+      atomicCAS(ab.status, 0, code);
+      return false;
     }
   }
   return true;
@@ -158,6 +185,17 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: A is read from tensor memory (lane = row, each 32-bit column holds two
+// consecutive 16-bit K elements), so an operand produced by the CUDA cores never passes through shared memory.
+__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrives (count 1) on the mbarrier once every MMA issued so far by this thread is done.
