@@ -20,7 +20,7 @@
 // instruction stream interleaves both kinds of work -- a warp that takes maxima while another one
 // exponentiates does not overlap with it.  The softmax pass is therefore a single sweep per block that
 // exponentiates against the running reference exponent m_ref of the PREVIOUS blocks,
-//     x = s * log2(e) + bias * log2(e) - m_ref  (fp32)  ->  fp16x2  ->  running max (fp16x2), ex2.approx.f16x2,
+//     x = s * log2(e) + bias' - m_ref  (fp32; bias' = bias * log2(e) as delivered)  ->  fp16x2  ->  running max (fp16x2), ex2.approx.f16x2,
 //     row sum (fp16x2 partial sums), P as fp16 into a swizzled K-major tile,
 // and only looks at the block maximum afterwards: if some row of the warp saw x > 8 (P > 256; fp16 would
 // overflow beyond 2^16), the warp takes the exact path -- fp32 row maximum from the logits still held in
@@ -28,7 +28,7 @@
 // the exact path.  With trained or random weights the repeat is rare after the first block, so the common
 // block costs one sweep.
 //
-// The pair bias arrives as bf16 [head][query][key] (key contiguous, row pitch a multiple of 8); TMA lays a
+// The pair bias arrives as bf16 [head][query][key], multiplied by log2(e) (key contiguous, row pitch a multiple of 8); TMA lays a
 // [128 queries][64 keys] tile out with the 128-byte swizzle, so the per-row 16-byte reads of the softmax
 // threads are bank-conflict free.
 #include <cstdlib>
@@ -325,16 +325,16 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             for (int c8 = 0; c8 < 8; ++c8) {
               const uint4 bq = *reinterpret_cast<const uint4*>(myBias + ((uint32_t(c8) ^ rsw) << 4));
               const int e = c8 * 8;
-              mx0 = fmaxf(mx0, __uint_as_float(r[e + 0]) + bf16_lo(bq.x));
-              mx1 = fmaxf(mx1, __uint_as_float(r[e + 1]) + bf16_hi(bq.x));
-              mx2 = fmaxf(mx2, __uint_as_float(r[e + 2]) + bf16_lo(bq.y));
-              mx3 = fmaxf(mx3, __uint_as_float(r[e + 3]) + bf16_hi(bq.y));
-              mx0 = fmaxf(mx0, __uint_as_float(r[e + 4]) + bf16_lo(bq.z));
-              mx1 = fmaxf(mx1, __uint_as_float(r[e + 5]) + bf16_hi(bq.z));
-              mx2 = fmaxf(mx2, __uint_as_float(r[e + 6]) + bf16_lo(bq.w));
-              mx3 = fmaxf(mx3, __uint_as_float(r[e + 7]) + bf16_hi(bq.w));
+              mx0 = fmaxf(mx0, fmaf(__uint_as_float(r[e + 0]), LOG2E, bf16_lo(bq.x)));
+              mx1 = fmaxf(mx1, fmaf(__uint_as_float(r[e + 1]), LOG2E, bf16_hi(bq.x)));
+              mx2 = fmaxf(mx2, fmaf(__uint_as_float(r[e + 2]), LOG2E, bf16_lo(bq.y)));
+              mx3 = fmaxf(mx3, fmaf(__uint_as_float(r[e + 3]), LOG2E, bf16_hi(bq.y)));
+              mx0 = fmaxf(mx0, fmaf(__uint_as_float(r[e + 4]), LOG2E, bf16_lo(bq.z)));
+              mx1 = fmaxf(mx1, fmaf(__uint_as_float(r[e + 5]), LOG2E, bf16_hi(bq.z)));
+              mx2 = fmaxf(mx2, fmaf(__uint_as_float(r[e + 6]), LOG2E, bf16_lo(bq.w)));
+              mx3 = fmaxf(mx3, fmaf(__uint_as_float(r[e + 7]), LOG2E, bf16_hi(bq.w)));
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * LOG2E;
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const bool grow = mx > m_ref + 8.f;
             if (__any_sync(0xffffffffu, grow)) {
               const float m_new = grow ? mx : m_ref;
@@ -369,8 +369,9 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             for (int e = 0; e < 4; ++e) {
               float x0 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e]), LOG2E, nm);
               float x1 = fmaf(__uint_as_float(r[c8 * 8 + 2 * e + 1]), LOG2E, nm);
-              x0 = fmaf(bf16_lo(bw[e]), LOG2E, x0);
-              x1 = fmaf(bf16_hi(bw[e]), LOG2E, x1);
+              // the bias tile is in log2 units already: one mixed-precision add per key, straight from the packed pair
+              asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+                  : "+f"(x0), "+f"(x1) : "r"(bw[e]));
               const __half2 xh = __floats2half2_rn(x0, x1);
               hm = __hmax2(hm, xh);
               uint32_t ph;
@@ -483,15 +484,15 @@ int launch_mext(Ctx* c, const float* mask, long long mask_ld, bf16* out, int B, 
   return check_launch(c, "mext_kernel");
 }
 
-// fp32 [H][S][S] -> bf16 [H][S][ldq] (same query-major order, padded row pitch): the layout the kernel's
-// pair-bias tensor map expects.
+// fp32 [H][S][S] -> bf16 [H][S][ldq] (same query-major order, padded row pitch) times log2(e): the operand the
+// kernel's pair-bias tensor map expects (the kernel works in base 2 and adds the tile as it is).
 __global__ void bias_convert_kernel(const float* __restrict__ in, bf16* __restrict__ out, long long rows, int S, int ldq) {
   const long long n = rows * ldq;
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
        idx += (long long)gridDim.x * blockDim.x) {
     const long long r = idx / ldq;
     const int k = int(idx % ldq);
-    out[idx] = __float2bfloat16(k < S ? in[r * S + k] : 0.f);
+    out[idx] = __float2bfloat16(k < S ? in[r * S + k] * 1.4426950408889634f : 0.f);
   }
 }
 

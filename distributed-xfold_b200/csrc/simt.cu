@@ -16,8 +16,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------------------------
 // y = LN(x) * gamma + beta  (gamma/beta may be null), rows of C bf16; optional
 // proj[h][row] = sum_c y[c] * pw[h][c]  (fp32, computed from the un-rounded y)
+// proj_bf16 (instead of proj) is the attention kernels' pair-bias operand: bf16, and multiplied by log2(e), because
+// the head-dim-32 attention kernel exponentiates in base 2 and adds the bias tile as it is.
 // optional modulation: y = sigmoid(scale[row % mod_rows][c]) * y + shift[row % mod_rows][c]  (AdaLN)
 // ---------------------------------------------------------------------------------------------
+constexpr float kBiasLog2e = 1.4426950408889634f;
+
 template <int C, int H>
 __global__ void __launch_bounds__(256)
 ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, long long ldy, long long rows,
@@ -135,7 +139,7 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
           const float tot = acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 1);
           const int h = (lane >> 1) & 15;
           if ((lane & 1) == 0) {
-            if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(tot);
+            if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(tot * kBiasLog2e);
             else proj[(long long)h * proj_plane + pidx[j]] = tot;
           }
         } else {
@@ -144,7 +148,7 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
 #pragma unroll
           for (int h = 0; h < H; ++h)
             if (lane == (h & 31)) {
-              if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(acc[h]);
+              if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(acc[h] * kBiasLog2e);
               else proj[(long long)h * proj_plane + pidx[j]] = acc[h];
             }
         }
@@ -279,7 +283,7 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
           const bool writer = (G == 16) ? true : ((l16 & 3) == 0);
           if (writer && valid[j]) {
             const long long o = (long long)(hb + hsel) * proj_plane + pidx[j];
-            if (proj_bf16) proj_bf16[o] = __float2bfloat16(acc[0]);
+            if (proj_bf16) proj_bf16[o] = __float2bfloat16(acc[0] * kBiasLog2e);
             else proj[o] = acc[0];
           }
         }

@@ -214,7 +214,10 @@ int xfold_trimul_output_fwd(xfold_ctx* ctx, const void* o, int ldo, const void* 
 /* x = act_norm(z) for R rows and the pair bias these rows contribute (nn/d_attention.py:61-62), bf16, laid out
  * [head][query][key]:
  * rows_are_keys = 0: the rows are query rows,  bias[h * plane + row_local * pitch + y];
- * rows_are_keys = 1: the rows are key rows x,  bias[h * plane + y * pitch + x_local]. */
+ * rows_are_keys = 1: the rows are key rows x,  bias[h * plane + y * pitch + x_local].
+ * The bias buffer is an operand of the attention kernel, not a result to read: its entries are the projected
+ * values times log2(e), because that kernel exponentiates in base 2 and adds the tile unchanged.  The same
+ * holds for plT below. */
 int xfold_triattn_bias_fwd(xfold_ctx* ctx, const void* z, int R, int N, const xfold_triattn_weights* w, void* x,
                            void* bias, int pitch, long long plane, int rows_are_keys, void* stream);
 /* z[R][N][128] += output_projection(gated attention(x)) along the second axis; bias: bf16 [4][N][ldq],
