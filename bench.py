@@ -259,6 +259,9 @@ def main():
         "layernorm": ("hbm", 2.0 * n * n * c * 2),
         "channel_ln": ("hbm", 2.0 * n * n * c * 2),
     }
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
+    # profiles/, taken at N = 1024; these kernels' traffic grows with N^2, so other sizes are scaled by (N / 1024)^2
+    ncu_traffic_n1024 = {"attention": 1.117e9 + 0.257e9, "trimul_contract": 0.537e9 + 0.235e9}
     top = max(per_kernel, key=lambda k: per_kernel[k]["ms_per_step"]) if per_kernel else None
 
     def roof(name):
@@ -271,7 +274,9 @@ def main():
         else:
             ach, pk, unit = work / sec / 1e9, hbm, "GB/s"
         return {"kernel": name, "bound": bound, "achieved": ach, "peak": pk, "unit": unit, "frac": ach / pk,
-                "traffic": None, "peak_source": which + (" (sustained)" if bound == "tensor" else ""),
+                "traffic": ncu_traffic_n1024[name] * (n / 1024.0) ** 2 if name in ncu_traffic_n1024 else None,
+                "traffic_unit": "bytes per launch (ncu, one launch at N=1024" + ("" if n == 1024 else ", scaled by N^2") + ")",
+                "peak_source": which + (" (sustained)" if bound == "tensor" else ""),
                 "share_of_step": per_kernel[name]["ms_per_step"] / ms_step}
 
     line = {"metric": "pairformer_ms_per_recycle", "value": ms_step, "unit": "ms", "n_gpus": 1, "steps": args.steps,

@@ -371,6 +371,42 @@ def pairformer_stack(state: State, pair, pair_mask, single, seq_mask, num_blocks
 # ----------------------------------------------------------------------------
 # seeded weight factory (Linear ~ N(0, 1/fan_in), LayerNorm gamma = 1, beta = 0)
 # ----------------------------------------------------------------------------
+# ---------------------------------------------------------------------------------------------
+# Diffusion head arithmetic around the transformer (nn/d_diffusion_head.py:172-227) and the sampler loop
+# (d_alphafold3.py:316-404), restated line by line in float64 loops over steps.  Parity unpinned: the reference's
+# loop is a method of the whole model (atom encoder / decoder and the noise schedule come from the absent xfold
+# package), so these functions are checked against the product's host code, not against a run of the reference.
+# ---------------------------------------------------------------------------------------------
+SIGMA_DATA = 16.0
+
+
+def diffusion_head_mix(positions_noisy, position_update, noise_level, atom_mask):
+    skip_scaling = SIGMA_DATA ** 2 / (noise_level ** 2 + SIGMA_DATA ** 2)
+    out_scaling = noise_level * SIGMA_DATA / torch.sqrt(noise_level ** 2 + SIGMA_DATA ** 2)
+    return (skip_scaling * positions_noisy + out_scaling * position_update) * atom_mask[..., None]
+
+
+def sampler_constants(noise_levels, gamma_0=0.8, gamma_min=1.0, noise_scale=1.003):
+    noise_level_prev = noise_levels[:-1]
+    noise_level = noise_levels[1:]
+    gamma = gamma_0 * (noise_level > gamma_min)
+    t_hat = noise_level_prev * (1 + gamma)
+    return noise_level, t_hat, noise_scale * torch.sqrt(t_hat ** 2 - noise_level_prev ** 2)
+
+
+def sample_diffusion(denoiser, noise_levels, positions0, step_scale=1.5):
+    """positions0: the initial draw, already multiplied by noise_levels[0]."""
+    noise_level, t_hat, noise_scale = sampler_constants(noise_levels)
+    positions = positions0
+    for step_idx in range(noise_level.shape[0]):
+        positions_noisy = positions + noise_scale[step_idx]
+        positions_denoised = denoiser(positions_noisy, t_hat[step_idx], step_idx)
+        grad = (positions_noisy - positions_denoised) / t_hat[step_idx]
+        d_t = noise_level[step_idx] - t_hat[step_idx]
+        positions = positions_noisy + step_scale * d_t * grad
+    return positions
+
+
 def _lin(g, out_f, in_f, bias=False):
     w = torch.randn(out_f, in_f, generator=g) / math.sqrt(in_f)
     b = torch.randn(out_f, generator=g) / math.sqrt(in_f) if bias else None
