@@ -33,6 +33,8 @@ def run_multi(args, world, rank, local_rank):
     z_h, s_h, pm_h, sm_h = O.make_inputs(3, n, pad_frac=0.1)
     sh = row_sharded.RowSharding(n)
     stages = row_sharded.CudaStages()
+    if os.environ.get("XFOLD_CHANNEL_SHARDED") in ("0", "1"):
+        sh.force_channel_sharded = os.environ["XFOLD_CHANNEL_SHARDED"] == "1"
     peer = sh.enable_peer_exchange(dev) and os.environ.get("XFOLD_NO_PEER") != "1"
     if not peer:
         sh.peer = None
@@ -125,6 +127,7 @@ def run_multi(args, world, rank, local_rank):
                         "d2h_bytes_per_step": (z_h.numel() + s_h.numel()) * 2 * world},
                 "roofline": roof, "model_tflops": flops_block(n) * nb / (ms_step * 1e-3) / 1e12,
                 "rank0_kernel_ms_per_step": kern_ms, "rank0_exchange_and_glue_ms_per_step": ms_step - kern_ms, "peer_memory_transpose": bool(peer),
+                "trimul_exchange": "channel slices (rows -> channels, product, rows back)" if sh.channel_sharded else "all-gather of b",
                 "kernels": per_kernel}
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -66,6 +66,7 @@ SIGNATURES = {
     "xfold_attention_pair_bias_core_fwd": (ci, [vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "xfold_trimul_project_fwd": (ci, [vp, vp, vp, ci, ci, C.POINTER(TriMulWeights), vp, vp, vp, vp, ci, vp]),
     "xfold_trimul_contract_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, vp, ci, vp]),
+    "xfold_trimul_contract_planes_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),
     "xfold_trimul_output_fwd": (ci, [vp, vp, ci, vp, ci, ci, C.POINTER(TriMulWeights), vp, vp, vp]),
     "xfold_triattn_bias_fwd": (ci, [vp, vp, ci, ci, C.POINTER(TriAttnWeights), vp, vp, ci, ll, ci, vp]),
     "xfold_triattn_core_scratch_bytes": (sz, [ci, ci, C.POINTER(sz)]),
@@ -77,6 +78,8 @@ SIGNATURES = {
     "xfold_triangle_attention_update_fwd": (ci, [vp, vp, vp, vp, ci, ci, C.POINTER(TriAttnWeights), vp, sz, vp]),
     "xfold_transition_update_fwd": (ci, [vp, vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp, sz, vp]),
     "xfold_transpose_scatter_fwd": (ci, [vp, vp, ci, ci, ci, C.POINTER(vp), C.POINTER(ci), ci, vp]),
+    "xfold_trimul_scatter_channels_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, C.POINTER(vp), C.POINTER(vp), ci, vp]),
+    "xfold_trimul_scatter_rows_fwd": (ci, [vp, vp, ci, ci, ci, ci, C.POINTER(vp), C.POINTER(ci), ci, vp]),
     "xfold_peer_barrier": (ci, [vp, C.POINTER(vp), ci, ci, ci, vp]),
     "xfold_transition_static_max_bytes": (sz, []),
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),

@@ -224,17 +224,18 @@ static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N
 // o[i][c][j] = sum_k a[i][c][k] * b[j][c][k]   (a: Ri rows, b: Nj rows, both [.][128][ld]; o: [Ri][128][ldo])
 // (chan, row) strides in elements: row-interleaved [rows][128][ld] has (ld, 128*ld); channel-major [128][rows][ld] has (rows*ld, ld)
 static int trimul_contract(Ctx* c, const bf16* a_, long long a_cs, long long a_rs, const bf16* b_, long long b_cs,
-                           long long b_rs, int Ri, int Nj, int K, bf16* o, long long o_cs, long long o_rs, cudaStream_t st) {
+                           long long b_rs, int Ri, int Nj, int K, bf16* o, long long o_cs, long long o_rs, cudaStream_t st,
+                           int channels = 128) {
   if (((a_cs | a_rs | b_cs | b_rs | o_cs | o_rs) & 7)) return fail(c, XFOLD_ERR_ARG, "contract: strides must be multiples of 8");
   CUtensorMap tA, tB;
-  if (!make_tmap_bf16_3d(&tA, a_, K, Ri, 128, a_rs, a_cs, 64, 128, 1) ||
-      !make_tmap_bf16_3d(&tB, b_, K, Nj, 128, b_rs, b_cs, 64, 256, 1))
+  if (!make_tmap_bf16_3d(&tA, a_, K, Ri, channels, a_rs, a_cs, 64, 128, 1) ||
+      !make_tmap_bf16_3d(&tB, b_, K, Nj, channels, b_rs, b_cs, 64, 256, 1))
     return fail(c, XFOLD_ERR_ARG, "contract: cannot encode tensor maps");
   GemmArgs a;
   a.M = Ri;
   a.N = Nj;
   a.K = K;
-  a.batches = 128;
+  a.batches = channels;
   a.b_batched = 1;
   a.tiles_m = (Ri + 127) / 128;
   a.tiles_n = (Nj + 255) / 256;
@@ -654,6 +655,13 @@ int xfold_trimul_contract_fwd(xfold_ctx* c, const void* a, const void* b_full, i
   if ((ld & 7) || (ldo & 7)) return fail(c, XFOLD_ERR_ARG, "contract: leading dimensions must be multiples of 8");
   return trimul_contract(c, (const bf16*)a, ld, (long long)128 * ld, (const bf16*)b_full, ld, (long long)128 * ld, R, Nj, K,
                          (bf16*)o, ldo, (long long)128 * ldo, (cudaStream_t)stream);
+}
+int xfold_trimul_contract_planes_fwd(xfold_ctx* c, const void* a, const void* b, int channels, int Ni, int Nj, int K, int ld,
+                                     void* o, int ldo, void* stream) {
+  if (!c || !a || !b || !o) return XFOLD_ERR_ARG;
+  if ((ld & 7) || (ldo & 7) || channels < 1) return fail(c, XFOLD_ERR_ARG, "contract: leading dimensions must be multiples of 8");
+  return trimul_contract(c, (const bf16*)a, (long long)Ni * ld, ld, (const bf16*)b, (long long)Nj * ld, ld, Ni, Nj, K, (bf16*)o,
+                         (long long)Ni * ldo, ldo, (cudaStream_t)stream, channels);
 }
 int xfold_trimul_output_fwd(xfold_ctx* c, const void* o, int ldo, const void* g, int R, int N, const xfold_trimul_weights* w,
                             void* x_scratch, void* z, void* stream) {

@@ -3,6 +3,12 @@
 //   transpose_scatter : distributed transpose of the row-sharded pair representation.  Every rank writes
 //                       each of its tokens z[i][j][:] (256 B) straight into the buffer of the rank that owns
 //                       column j, at zT[j_local][i][:], so the whole exchange is one kernel per rank.
+//   channel_scatter   : row shard -> channel shard of the TriangleMultiplication operands.  Rank p holds a / b for its
+//                       rows and all 128 channels; the contraction is independent per channel, so each rank takes
+//                       128 / P channels for ALL rows: row (i, c) of 2 * ld bytes goes to rank c / (128 / P).  For
+//                       P >= 4 this moves less than gathering b on every rank ((P-1)/P * 3 N^2 c / P elements per
+//                       rank instead of (P-1)/P * N^2 c).
+//   row_scatter       : the way back: the contraction output of a rank's channels, row i to the rank that owns i.
 //   peer_barrier      : release / acquire flag barrier between the ranks.  The wait is bounded: when it runs
 //                       out the kernel records XF_ERR_WAIT_PEER in the status word and returns.
 #include "internal.h"
@@ -34,6 +40,48 @@ transpose_scatter_kernel(const bf16* __restrict__ z, int R, int N, int row0, Pee
     const uint4 v = *reinterpret_cast<const uint4*>(z + tok * 128 + part * 8);
     bf16* dst = reinterpret_cast<bf16*>(pt.ptr[q]) + ((long long)(j - pt.start[q]) * N + (row0 + i)) * 128 + part * 8;
     *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+// One warp copies one row of ld elements (16-byte vectors).  src: [R][128][ld] (row i, channel c);
+// dst on rank q = c / cq: planes [cq][N][ld], row (c % cq, row0 + i).
+__global__ void __launch_bounds__(256)
+channel_scatter_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, int R, int N, int ld, int row0, int cq,
+                       PeerTable pa, PeerTable pb) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long rows = (long long)R * 128 * 2;
+  const int vecs = ld >> 3;
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < rows; w += warps) {
+    const int which = int(w & 1);
+    const long long rc = w >> 1;
+    const int c = int(rc & 127), i = int(rc >> 7);
+    const int q = c / cq;
+    const uint4* src = reinterpret_cast<const uint4*>((which ? b : a) + rc * ld);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(which ? pb.ptr[q] : pa.ptr[q]) +
+                                          ((long long)(c - q * cq) * N + row0 + i) * ld);
+    for (int v = lane; v < vecs; v += 32) dst[v] = src[v];
+  }
+}
+
+// src: planes [cq][N][ldo] (local channel c, row i); dst on the rank p that owns row i: [R_p][128][ldo], row
+// (i - start[p], chan0 + c).
+__global__ void __launch_bounds__(256)
+row_scatter_kernel(const bf16* __restrict__ o, int cq, int N, int ldo, int chan0, PeerTable pt) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  const long long rows = (long long)cq * N;
+  const int vecs = ldo >> 3;
+  for (long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); w < rows; w += warps) {
+    const int i = int(w % N), c = int(w / N);
+    int p = 0;
+#pragma unroll
+    for (int r = 1; r < MAX_PEERS; ++r)
+      if (r < pt.world && i >= pt.start[r]) p = r;
+    const uint4* src = reinterpret_cast<const uint4*>(o + w * ldo);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(pt.ptr[p]) +
+                                          ((long long)(i - pt.start[p]) * 128 + chan0 + c) * ldo);
+    for (int v = lane; v < vecs; v += 32) dst[v] = src[v];
   }
 }
 
@@ -83,6 +131,50 @@ int xfold_transpose_scatter_fwd(xfold_ctx* cx, const void* z, int R, int N, int 
   ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
   transpose_scatter_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)z, R, N, row0, pt);
   return check_launch(c, "transpose_scatter_kernel");
+}
+
+int xfold_trimul_scatter_channels_fwd(xfold_ctx* cx, const void* a, const void* b, int R, int N, int ld, int row0,
+                                      void* const* peer_a, void* const* peer_b, int world, void* stream) {
+  Ctx* c = reinterpret_cast<Ctx*>(cx);
+  if (!c || !a || !b || !peer_a || !peer_b) return XFOLD_ERR_ARG;
+  if (world < 1 || world > MAX_PEERS || 128 % world) return fail(c, XFOLD_ERR_ARG, "channel scatter: the rank count must divide 128 (1, 2, 4, 8), got %d", world);
+  if (ld & 7) return fail(c, XFOLD_ERR_ARG, "channel scatter: ld must be a multiple of 8");
+  if (R <= 0 || N <= 0) return XFOLD_OK;
+  PeerTable pa, pb;
+  pa.world = pb.world = world;
+  for (int q = 0; q < MAX_PEERS; ++q) {
+    pa.ptr[q] = q < world ? peer_a[q] : nullptr;
+    pb.ptr[q] = q < world ? peer_b[q] : nullptr;
+  }
+  for (int q = 0; q <= MAX_PEERS; ++q) pa.start[q] = pb.start[q] = 0;
+  const long long rows = (long long)R * 128 * 2;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)c->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
+  channel_scatter_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)a, (const bf16*)b, R, N, ld, row0,
+                                                                         128 / world, pa, pb);
+  return check_launch(c, "channel_scatter_kernel");
+}
+
+int xfold_trimul_scatter_rows_fwd(xfold_ctx* cx, const void* o, int channels, int chan0, int N, int ldo,
+                                  void* const* peer_o, const int* row_starts, int world, void* stream) {
+  Ctx* c = reinterpret_cast<Ctx*>(cx);
+  if (!c || !o || !peer_o || !row_starts) return XFOLD_ERR_ARG;
+  if (world < 1 || world > MAX_PEERS) return fail(c, XFOLD_ERR_ARG, "row scatter: 1 to %d ranks supported, got %d", MAX_PEERS, world);
+  if ((ldo & 7) || chan0 < 0 || chan0 + channels > 128) return fail(c, XFOLD_ERR_ARG, "row scatter: bad channel range or ldo");
+  if (channels <= 0 || N <= 0) return XFOLD_OK;
+  PeerTable pt;
+  pt.world = world;
+  for (int q = 0; q < MAX_PEERS; ++q) pt.ptr[q] = q < world ? peer_o[q] : nullptr;
+  for (int q = 0; q <= MAX_PEERS; ++q) pt.start[q] = q <= world ? row_starts[q] : N;
+  const long long rows = (long long)channels * N;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)c->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
+  row_scatter_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)o, channels, N, ldo, chan0, pt);
+  return check_launch(c, "row_scatter_kernel");
 }
 
 int xfold_peer_barrier(xfold_ctx* cx, void* const* peer_flags, int me, int world, int epoch, void* stream) {

@@ -392,6 +392,19 @@ def stage_trimul_contract(a: torch.Tensor, b_full: torch.Tensor, n: int) -> torc
     return o
 
 
+def stage_trimul_contract_planes(a: torch.Tensor, b: torch.Tensor, n: int) -> torch.Tensor:
+    """Channel-major planes: o[c, i, j] = sum_k a[c, i, k] * b[c, j, k] over the first n entries of k."""
+    _need_cuda(a, b)
+    dev = _dev(a)
+    ch, ni, ld = a.shape
+    nj = b.shape[1]
+    ldo = _pad8(nj)
+    o = torch.empty(ch, ni, ldo, dtype=BF16, device=a.device)
+    rc = load().xfold_trimul_contract_planes_fwd(ctx(dev), _ptr(a), _ptr(b), ch, ni, nj, n, ld, _ptr(o), ldo, _stream(dev))
+    check(rc, dev, "xfold_trimul_contract_planes_fwd")
+    return o
+
+
 def stage_trimul_output(o: torch.Tensor, g: torch.Tensor, z: torch.Tensor, w: PackedTriMul) -> None:
     _need_cuda(o, g, z)
     dev = _dev(z)

@@ -7,8 +7,9 @@ reference's sharded TriMul, nn/d_triangle_multiplication.py:48-99, is written bu
 Per block and rank, with R = rows held by the rank and zT the row shard of the transposed pair
 representation (zT[j][i] = z[i][j]):
 
-    z   : TriMul outgoing        gather b rows            (all-gather, N*N*c / P elements per peer)
-    zT  : TriMul incoming        gather b rows            'ckj,cki->cij' on z is 'cik,cjk->cij' on zT
+    z   : TriMul outgoing        gather b rows            (all-gather, N*N*c / P elements per peer), or from 4 ranks
+                                                          on: a, b to channel slices, product, output rows back
+    zT  : TriMul incoming        the same                 'ckj,cki->cij' on z is 'cik,cjk->cij' on zT
     z   : TriAttn starting node  gather the pair bias     (4 * N * N bf16 in total, [head, query, key])
     zT  : TriAttn ending node    gather the pair bias, then pair Transition (token-local)
     z   : pair logits, gathered; the single path is replicated on every rank (it is < 1 % of the work)
@@ -99,6 +100,39 @@ class RowSharding:
             self.peer_error = repr(e)
             return False
 
+    # -- channel-sharded TriangleMultiplication contraction -------------------------------------------
+    @property
+    def channel_sharded(self) -> bool:
+        """The contraction 'cik,cjk->cij' is independent per channel.  Gathering b on every rank moves
+        (P-1)/P * N^2 c elements into each rank; handing every rank 128 / P channels of a and b for ALL rows and
+        sending its output rows back moves (P-1)/P * 3 N^2 c / P: less from P = 4 on."""
+        forced = getattr(self, "force_channel_sharded", None)
+        if forced is not None:
+            return bool(forced) and 128 % self.world == 0 and self.world > 1
+        return self.world >= 4 and 128 % self.world == 0
+
+    def rows_to_channels(self, a: torch.Tensor, b: torch.Tensor):
+        """a, b [R_me, 128, ld] -> planes [128 / P, N, ld] of this rank's channels, all rows."""
+        if getattr(self, "peer", None) is not None and a.is_cuda:
+            return self.peer.rows_to_channels(a, b)
+        cq = 128 // self.world
+        out = []
+        for t in (a, b):
+            send = [t[:, q * cq:(q + 1) * cq, :].transpose(0, 1).contiguous() for q in range(self.world)]   # [cq, R_me, ld]
+            recv = [t.new_empty((cq, sz, t.shape[2])) for sz in self.sizes]
+            _exchange(send, recv, self.group)
+            out.append(torch.cat(recv, dim=1))
+        return out[0], out[1]
+
+    def channels_to_rows(self, o: torch.Tensor) -> torch.Tensor:
+        """o [128 / P, N, ldo] of this rank's channels -> [R_me, 128, ldo] of this rank's rows, all channels."""
+        if getattr(self, "peer", None) is not None and o.is_cuda:
+            return self.peer.channels_to_rows(o)
+        send = [o[:, sl, :].transpose(0, 1).contiguous() for sl in self.slices]                              # [R_q, cq, ldo]
+        recv = [o.new_empty((self.r, o.shape[0], o.shape[2])) for _ in range(self.world)]
+        _exchange(send, recv, self.group)
+        return torch.cat(recv, dim=1)
+
     def transpose(self, z: torch.Tensor) -> torch.Tensor:
         """Row shard of z [R_me, N, c] -> row shard of z^T: out[j_local, i] = z_global[i, j_global]."""
         if self.world == 1:
@@ -139,6 +173,8 @@ class PeerExchange:
         self.starts = [sl.start for sl in sh.slices] + [sh.n]
         self.k = 0
         self.epoch = 0
+        self.symm, self.group = symm, group
+        self.planes = None  # buffers of the channel-sharded contraction, made on first use
         torch.cuda.synchronize(device)
         dist.barrier(group=sh.group)  # every rank's flags are zero before anyone signals
 
@@ -155,6 +191,48 @@ class PeerExchange:
         return self.bufs[k][: sh.r * sh.n * self.c].view(sh.r, sh.n, self.c)
 
 
+    # -- channel-sharded contraction: operand planes and output rows in peer-mapped buffers ------------
+    def _plane_buffers(self, ld: int, ldo: int, device):
+        sh = self.sh
+        if self.planes is not None and self.planes["ld"] == ld and self.planes["ldo"] == ldo:
+            return self.planes
+        cq, rmax = 128 // sh.world, max(sh.sizes)
+        bufs = {"ld": ld, "ldo": ldo}
+        for name, numel in (("a", cq * sh.n * ld), ("b", cq * sh.n * ld), ("o", rmax * 128 * ldo)):
+            t = self.symm.empty(numel, dtype=torch.bfloat16, device=device)
+            if ld != sh.n or ldo != sh.n:
+                t.zero_()  # pad columns stay zero: the scatters only ever write whole rows of the same pitch
+            h = self.symm.rendezvous(t, self.group)
+            off = t.data_ptr() - int(h.buffer_ptrs[sh.rank])
+            bufs[name] = t
+            bufs[name + "_ptrs"] = [int(p) + off for p in h.buffer_ptrs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group=sh.group)
+        self.planes = bufs
+        return bufs
+
+    def _barrier(self, device):
+        self.epoch += 1
+        self.ops.peer_barrier(self.flag_ptrs, self.sh.rank, self.sh.world, self.epoch, device)
+
+    def rows_to_channels(self, a: torch.Tensor, b: torch.Tensor):
+        sh = self.sh
+        ld = a.shape[2]
+        p = self._plane_buffers(ld, (sh.n + 7) // 8 * 8, a.device)
+        self.ops.scatter_channels(a.contiguous(), b.contiguous(), sh.n, sh.rows.start, p["a_ptrs"], p["b_ptrs"])
+        self._barrier(a.device)
+        cq = 128 // sh.world
+        return p["a"].view(cq, sh.n, ld), p["b"].view(cq, sh.n, ld)
+
+    def channels_to_rows(self, o: torch.Tensor) -> torch.Tensor:
+        sh = self.sh
+        p = self._plane_buffers(self.planes["ld"], o.shape[2], o.device)
+        cq = 128 // sh.world
+        self.ops.scatter_rows(o.contiguous(), sh.rank * cq, p["o_ptrs"], self.starts)
+        self._barrier(o.device)
+        return p["o"][: sh.r * 128 * o.shape[2]].view(sh.r, 128, o.shape[2])
+
+
 class CudaStages:
     """Stage backend on the C ABI (sm_100a kernels)."""
 
@@ -166,6 +244,15 @@ class CudaStages:
         return getattr(self.ops, "stage_" + name)
 
 
+def _contract(sh: RowSharding, stages, a: torch.Tensor, b: torch.Tensor, n: int) -> torch.Tensor:
+    """o[i, c, j] = sum_k a[i, c, k] b[j, c, k] for this rank's rows i: either against the gathered rows of b, or, from
+    four ranks on, per channel slice on all rows with an exchange before and after (see RowSharding.channel_sharded)."""
+    if sh.channel_sharded:
+        ap, bp = sh.rows_to_channels(a, b)
+        return sh.channels_to_rows(stages.trimul_contract_planes(ap, bp, n))
+    return stages.trimul_contract(a, sh.gather_rows(b), n)
+
+
 def pairformer_block(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch.Tensor], pair_mask: torch.Tensor,
                      pair_mask_t: torch.Tensor, seq_mask: Optional[torch.Tensor], w) -> tuple:
     """One block.  z: this rank's rows [R, N, c] (updated, returned); s: replicated [N, c_s];
@@ -174,14 +261,12 @@ def pairformer_block(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch
     ldq = (n + 7) // 8 * 8
     # TriangleMultiplication, outgoing edges, on z
     a, b, g = stages.trimul_project(z, pair_mask[rows], w.tri_out)
-    o = stages.trimul_contract(a, sh.gather_rows(b), n)
-    stages.trimul_output(o, g, z, w.tri_out)
+    stages.trimul_output(_contract(sh, stages, a, b, n), g, z, w.tri_out)
     # incoming edges: the same product on the transposed layout
     zt = sh.transpose(z)
     a, b, g = stages.trimul_project(zt, pair_mask_t[rows], w.tri_in)
-    o = stages.trimul_contract(a, sh.gather_rows(b), n)
-    stages.trimul_output(o, g, zt, w.tri_in)
-    del a, b, g, o
+    stages.trimul_output(_contract(sh, stages, a, b, n), g, zt, w.tri_in)
+    del a, b, g
     # TriangleAttention, starting node, on z: the local rows are QUERY rows of the bias [head, query, key]
     z = sh.transpose(zt)
     x, bias_loc = stages.triattn_bias(z, w.att_start, False)          # [4, R, ldq]

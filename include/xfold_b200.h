@@ -208,6 +208,12 @@ int xfold_trimul_project_fwd(xfold_ctx* ctx, const void* z, const float* mask, i
 /* o[i][c][j] = sum_k a[i][c][k] * b_full[j][c][k]  ('cik,cjk->cij' on the row shard of a against all rows of b) */
 int xfold_trimul_contract_fwd(xfold_ctx* ctx, const void* a, const void* b_full, int R, int Nj, int K, int ld, void* o,
                               int ldo, void* stream);
+/* The same product on channel-major planes: a [channels][Ni][ld], b [channels][Nj][ld] -> o [channels][Ni][ldo].
+ * Used by the channel-sharded form of the multi-GPU contraction: the product is independent per channel
+ * (the 'c' of 'cik,cjk->cij', nn/d_triangle_multiplication.py:122-124), so a rank may take a slice of the
+ * channels for all rows instead of gathering b for its rows (nn/d_triangle_multiplication.py:74-79). */
+int xfold_trimul_contract_planes_fwd(xfold_ctx* ctx, const void* a, const void* b, int channels, int Ni, int Nj, int K,
+                                     int ld, void* o, int ldo, void* stream);
 /* z[R][N][128] += output_projection(center_norm(o)) * sigmoid(g)   (nn/d_triangle_multiplication.py:92-99) */
 int xfold_trimul_output_fwd(xfold_ctx* ctx, const void* o, int ldo, const void* g, int R, int N,
                             const xfold_trimul_weights* w, void* x_scratch, void* z, void* stream);
@@ -245,6 +251,17 @@ int xfold_single_update_fwd(xfold_ctx* ctx, void* s, const void* plT, int ldq, c
  * (ShardInfo rule, distribute_utils.py:101-128).  Plain stores over NVLink, no multicast. */
 int xfold_transpose_scatter_fwd(xfold_ctx* ctx, const void* z, int R, int N, int row0, void* const* peer_bufs,
                                 const int* col_starts, int world, void* stream);
+/* Row shard -> channel shard of the TriangleMultiplication operands, in place of the all-gather of b
+ * (nn/d_triangle_multiplication.py:74-79): a, b are this rank's [R][128][ld] operands (rows row0 ..); row (i, c)
+ * goes to rank q = c / (128 / world), into its planes peer_a[q] / peer_b[q] = [128 / world][N][ld] at
+ * (c % (128 / world), row0 + i).  world must divide 128.  Plain 16-byte stores over NVLink. */
+int xfold_trimul_scatter_channels_fwd(xfold_ctx* ctx, const void* a, const void* b, int R, int N, int ld, int row0,
+                                      void* const* peer_a, void* const* peer_b, int world, void* stream);
+/* The way back: o = [channels][N][ldo] planes of this rank's channels chan0 .. chan0 + channels - 1; row (c, i) goes
+ * to the rank p that owns pair row i (row_starts: world + 1 offsets), into peer_o[p] = [R_p][128][ldo] at
+ * (i - row_starts[p], chan0 + c): the layout xfold_trimul_output_fwd reads. */
+int xfold_trimul_scatter_rows_fwd(xfold_ctx* ctx, const void* o, int channels, int chan0, int N, int ldo,
+                                  void* const* peer_o, const int* row_starts, int world, void* stream);
 /* Flag barrier between the ranks (the reference uses dist.barrier, run_inference.py:154-245): rank `me`
  * stores `epoch` into slot `me` of every rank's flag array (peer_flags[q], 8 ints, zero-initialised) and
  * waits until all slots of its own array reached `epoch`.  The wait is bounded; a time-out is reported by

@@ -37,6 +37,9 @@ class OracleStages:
     def trimul_contract(self, a, b_full, n):
         return torch.einsum("ick,jck->icj", a[..., :n], b_full[..., :n])
 
+    def trimul_contract_planes(self, a, b, n):
+        return torch.einsum("cik,cjk->cij", a[..., :n], b[..., :n])
+
     def trimul_output(self, o, g, z, w):
         st, p = w
         y = self.O.layer_norm(o.permute(0, 2, 1), st.get(p + "center_norm.weight"), st.get(p + "center_norm.bias"))

@@ -13,7 +13,7 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, n, ret):
+def _worker(rank, world, port, n, ret, channel_sharded=None):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import __graft_entry__ as ge
@@ -28,6 +28,9 @@ def _worker(rank, world, port, n, ret):
     st = O.make_pairformer_block_state(g, "")
     z, s, pm, sm = O.make_inputs(6, n, pad_frac=0.15)
     sh = row_sharded.RowSharding(n)
+    if channel_sharded is not None:
+        sh.force_channel_sharded = channel_sharded
+        assert sh.channel_sharded == channel_sharded
     zs, ss = z[sh.rows].clone(), s.clone()
     with torch.no_grad():
         zs, ss = row_sharded.pairformer_block(sh, stage_double.OracleStages(O), zs, ss, pm, pm.t().contiguous(), sm,
@@ -39,12 +42,14 @@ def _worker(rank, world, port, n, ret):
     cleanup()
 
 
-@pytest.mark.parametrize("world,n", [(2, 24), (3, 20), (2, 17)])
-def test_row_sharded_block_matches_oracle(pkg, oracle, world, n):
+@pytest.mark.parametrize("world,n,channel_sharded", [(2, 24, None), (3, 20, None), (2, 17, None), (2, 17, True), (4, 22, None)])
+def test_row_sharded_block_matches_oracle(pkg, oracle, world, n, channel_sharded):
+    """channel_sharded: the contraction on channel slices (rows -> channels exchange, product, rows back) instead of the
+    gather of b; it is the default from 4 ranks on, and forced at 2 ranks with a ragged shard."""
     from distributed_xfold_b200.distribute_utils import find_free_port
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(world, find_free_port(), n, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, find_free_port(), n, ret, channel_sharded), nprocs=world, join=True)
     g = torch.Generator().manual_seed(5)
     st = oracle.make_pairformer_block_state(g, "")
     z, s, pm, sm = oracle.make_inputs(6, n, pad_frac=0.15)

@@ -47,7 +47,7 @@ def test_row_sharded_block_single_shard(ops, oracle, n, pad):
     assert relf((zd.float().cpu() - z.float())[pm > 0], (rz - z.float())[pm > 0]) < 3e-2
 
 
-def _rank_main(rank, world, port, n, pad, use_peer, ret):
+def _rank_main(rank, world, port, n, pad, use_peer, channel, ret):
     sys.path.insert(0, ROOT)
     import __graft_entry__ as ge
     ge.load_package()
@@ -61,6 +61,8 @@ def _rank_main(rank, world, port, n, pad, use_peer, ret):
     z, s, pm, sm = O.make_inputs(901 + n, n, pad_frac=pad)
     w = ops.PackedPairformerBlock(st, "", f"cuda:{rank}")
     sh = row_sharded.RowSharding(n)
+    if channel is not None:
+        sh.force_channel_sharded = channel
     if use_peer:
         assert sh.enable_peer_exchange(f"cuda:{rank}"), getattr(sh, "peer_error", "")
     zd = z[sh.rows].to(BF).cuda().contiguous()
@@ -75,17 +77,18 @@ def _rank_main(rank, world, port, n, pad, use_peer, ret):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_peer", [False, True])
+@pytest.mark.parametrize("use_peer,channel", [(False, None), (True, None), (True, True), (False, True)])
 @pytest.mark.parametrize("n,pad", [(128, 0.0), (131, 0.1)])
-def test_row_sharded_block_nccl_ranks(pkg, oracle, n, pad, use_peer):
-    """use_peer: the distributed transposes run as one peer-memory kernel per rank plus a bounded flag barrier;
-    otherwise as pairwise send/recv."""
+def test_row_sharded_block_nccl_ranks(pkg, oracle, n, pad, use_peer, channel):
+    """use_peer: the distributed transposes (and the exchanges of the channel-sharded contraction) run as peer-memory
+    kernels of the library plus a bounded flag barrier; otherwise as pairwise send/recv.
+    channel: force the channel-sharded TriangleMultiplication contraction (the default from 4 ranks on)."""
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs two or more GPUs")
     from distributed_xfold_b200.distribute_utils import find_free_port
     st, z, s, pm, sm, rz, rs = _reference(oracle, n, 900 + n, pad)
     ret = mp.Manager().dict()
-    mp.spawn(_rank_main, args=(world, find_free_port(), n, pad, use_peer, ret), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, find_free_port(), n, pad, use_peer, channel, ret), nprocs=world, join=True)
     assert relf(ret["z"][pm > 0], rz[pm > 0]) < 2e-2
     assert relf(ret["s"][sm > 0], rs[sm > 0]) < 2e-2
