@@ -299,7 +299,7 @@ static int launch_ln128(Ctx* c, const bf16* x, long long ldx, bf16* y, long long
   if ((ldx & 7) || (ldy & 7)) return fail(c, XFOLD_ERR_ARG, "layernorm(128): row strides must be multiples of 8 elements");
   const int slots = (H == 0) ? 4 : (H == 4 ? 2 : 1);
   long long blocks = (rows + 16 * slots - 1) / (16 * slots);  // 8 warps x 2 rows x slots per pass
-  const long long cap = (long long)c->sm_count * 8;
+  const long long cap = (long long)c->sm_count * 3;  // one wave of resident CTAs (3 per SM): the loop is grid-strided
   if (blocks > cap) blocks = cap;
   if (blocks <= 0) return XFOLD_OK;
   const size_t sm = (size_t)H * 128 * sizeof(float);
@@ -438,7 +438,7 @@ int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_st
   const long long ntiles = (long long)R * ((N + CMLN_TOK - 1) / CMLN_TOK);
   if (ntiles <= 0) return XFOLD_OK;
   long long blocks = ntiles;
-  const long long cap = (long long)c->sm_count * 8;
+  const long long cap = (long long)c->sm_count * 3;  // one wave of resident CTAs (3 per SM): the loop is grid-strided
   if (blocks > cap) blocks = cap;
   ProfScope ps(c, XFOLD_K_CHANNEL_LN, st);
   cm_ln_kernel<<<(int)blocks, 256, 0, st>>>(in, chan_stride, row_stride, R, N, out, gamma, beta, eps);
