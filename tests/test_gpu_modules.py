@@ -158,3 +158,60 @@ def test_pairformer_block_golden(ops, oracle, golden):
     ops.synchronize_and_check()
     assert relf(zd.float().cpu()[pm > 0], ref_z[pm > 0]) < 2e-2
     assert relf(sd.float().cpu()[sm > 0], ref_s[sm > 0]) < 2e-2
+
+
+def with_affine_norms(state, seed):
+    """The factories initialise every LayerNorm with gamma = 1, beta = 0 (the reference's defaults); real checkpoints
+    do not.  Perturb every 1-D parameter (LayerNorm scales and offsets, and the few Linear biases)."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for k, v in state.items():
+        if v.ndim == 1 and k.endswith(".weight"):
+            out[k] = 1.0 + 0.3 * torch.randn(v.shape, generator=g)
+        elif v.ndim == 1 and k.endswith(".bias"):
+            out[k] = v + 0.3 * torch.randn(v.shape, generator=g)
+        else:
+            out[k] = v
+    return out
+
+
+@pytest.mark.parametrize("n,pad", [(40, 0.0), (128, 0.1), (200, 0.1)])
+def test_pairformer_block_with_affine_layernorms(ops, oracle, n, pad):
+    """Every LayerNorm of the block with non-trivial scale and offset (pad / tile-tail sizes included)."""
+    g = torch.Generator().manual_seed(1600 + n)
+    st = with_affine_norms(oracle.make_pairformer_block_state(g, ""), 1700 + n)
+    z, s, pm, sm = make_pair(oracle, n, 1800 + n, pad)
+    rz, rs = oracle.pairformer_block(rounded(st), "", z.float(), pm, s.float(), sm)
+    w = ops.PackedPairformerBlock(st, "", "cuda")
+    zd, sd = z.cuda().contiguous(), s.cuda().contiguous()
+    ops.pairformer_block_(zd, sd, pm.cuda(), sm.cuda(), w)
+    ops.synchronize_and_check()
+    check_update(z, zd, rz, pm > 0)
+    check_update(s, sd, rs, sm > 0)
+
+
+@pytest.mark.parametrize("outgoing", [True, False])
+def test_triangle_multiplication_with_affine_layernorms(ops, oracle, outgoing):
+    n = 128
+    g = torch.Generator().manual_seed(1900)
+    st = with_affine_norms(oracle.make_trimul_state(g, ""), 1901)
+    z = (2.0 * torch.randn(n, n, 128, generator=g) + 0.7).to(BF)   # rows with a mean well away from zero
+    mask = (torch.rand(n, n, generator=g) > 0.2).float()
+    ref = z.float() + oracle.triangle_multiplication(rounded(st), "", z.float(), mask, outgoing)
+    w = ops.PackedTriMul(st, "", "cuda")
+    zd = z.cuda().contiguous()
+    ops.triangle_multiplication_(zd, mask.cuda(), w, outgoing)
+    ops.synchronize_and_check()
+    check_update(z, zd, ref)
+
+
+def test_transition_with_affine_layernorm(ops, oracle):
+    g = torch.Generator().manual_seed(1950)
+    st = with_affine_norms(oracle.make_transition_state(g, "", 128), 1951)
+    x = (1.5 * torch.randn(40, 50, 128, generator=g) - 0.5).to(BF)
+    ref = x.float() + oracle.transition(rounded(st), "", x.float())
+    w = ops.PackedTransition(st, "", "cuda")
+    xd = x.cuda().contiguous()
+    ops.transition_(xd, w)
+    ops.synchronize_and_check()
+    check_update(x, xd, ref)
