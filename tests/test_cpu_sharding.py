@@ -42,7 +42,7 @@ def _worker(rank, world, port, n, ret, channel_sharded=None):
     cleanup()
 
 
-@pytest.mark.parametrize("world,n,channel_sharded", [(2, 24, None), (3, 20, None), (2, 17, None), (2, 17, True), (4, 22, None)])
+@pytest.mark.parametrize("world,n,channel_sharded", [(2, 24, None), (3, 20, None), (2, 17, None), (2, 17, True), (4, 22, None), (8, 30, None)])
 def test_row_sharded_block_matches_oracle(pkg, oracle, world, n, channel_sharded):
     """channel_sharded: the contraction on channel slices (rows -> channels exchange, product, rows back) instead of the
     gather of b; it is the default from 4 ranks on, and forced at 2 ranks with a ragged shard."""
