@@ -356,34 +356,50 @@ int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy,
 // ---------------------------------------------------------------------------------------------
 constexpr int CMLN_TOK = 128;
 constexpr int CMLN_PITCH = CMLN_TOK + 8;  // elements; keeps every row 16-byte aligned
+constexpr size_t CMLN_TILE_BYTES = (size_t)128 * CMLN_PITCH * sizeof(bf16);
+constexpr size_t CMLN_SMEM = 2 * CMLN_TILE_BYTES + 2 * 4 * CMLN_TOK * sizeof(float);
+
+// The tile of the NEXT iteration is fetched with cp.async (global -> shared without passing through registers) while
+// the current one is normalised and stored, so loads stay in flight through the compute and store phases.
 __global__ void __launch_bounds__(256, 3)
 cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, long long row_stride, int R, int N,
              bf16* __restrict__ out, const float* __restrict__ gamma, const float* __restrict__ beta, float eps) {
-  __shared__ __align__(16) bf16 tile[128][CMLN_PITCH];
-  __shared__ float psum[4][CMLN_TOK], psq[4][CMLN_TOK];
+  extern __shared__ __align__(16) uint8_t cmln_smem[];
+  bf16 (*tiles)[128][CMLN_PITCH] = reinterpret_cast<bf16 (*)[128][CMLN_PITCH]>(cmln_smem);
+  float (*psum)[CMLN_TOK] = reinterpret_cast<float (*)[CMLN_TOK]>(cmln_smem + 2 * CMLN_TILE_BYTES);
+  float (*psq)[CMLN_TOK] = psum + 4;
   const int tiles_j = (N + CMLN_TOK - 1) / CMLN_TOK;
   const long long ntiles = (long long)R * tiles_j;
   const bool vec_ok = ((chan_stride | row_stride) & 7) == 0;
-  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+  // 128 channel rows x 128 tokens: 16 x 16-byte pieces per row
+  auto fetch = [&](long long t, int buf) {
     const int i = int(t / tiles_j);
     const int j0 = int(t % tiles_j) * CMLN_TOK;
-    __syncthreads();
-    // 128 channel rows x 128 tokens: 16 x 16-byte loads per row
     for (int idx = threadIdx.x; idx < 128 * 16; idx += 256) {
       const int ch = idx >> 4, w = idx & 15;
       const int j = j0 + 8 * w;
       const bf16* src = in + ch * chan_stride + (long long)i * row_stride + j;
-      uint4 u = make_uint4(0, 0, 0, 0);
-      if (vec_ok && j + 7 < N) u = *reinterpret_cast<const uint4*>(src);
-      else {
+      bf16* dst = &tiles[buf][ch][8 * w];
+      if (vec_ok && j + 7 < N) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+      } else {
         bf16 tmp[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) tmp[e] = (j + e < N) ? src[e] : __float2bfloat16(0.f);
-        u = *reinterpret_cast<uint4*>(tmp);
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<uint4*>(tmp);
       }
-      *reinterpret_cast<uint4*>(&tile[ch][8 * w]) = u;
     }
-    __syncthreads();
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  int buf = 0;
+  if ((long long)blockIdx.x < ntiles) fetch(blockIdx.x, 0);
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, buf ^= 1) {
+    const int i = int(t / tiles_j);
+    const int j0 = int(t % tiles_j) * CMLN_TOK;
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // tile t has landed for every thread; everybody is done with the other buffer and with psum
+    if (t + gridDim.x < ntiles) fetch(t + gridDim.x, buf ^ 1);
+    bf16 (*tile)[CMLN_PITCH] = tiles[buf];
     // thread = (token pair tp, quarter of the channels): a warp reads 32 consecutive 4-byte words per channel row
     const int tp = threadIdx.x & 63, part = threadIdx.x >> 6;
     float v0[32], v1[32];
@@ -431,6 +447,7 @@ cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, long long row_s
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_stride, int R, int N, bf16* out,
@@ -441,7 +458,13 @@ int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_st
   const long long cap = (long long)c->sm_count * 3;  // one wave of resident CTAs (3 per SM): the loop is grid-strided
   if (blocks > cap) blocks = cap;
   ProfScope ps(c, XFOLD_K_CHANNEL_LN, st);
-  cm_ln_kernel<<<(int)blocks, 256, 0, st>>>(in, chan_stride, row_stride, R, N, out, gamma, beta, eps);
+  static bool attr_done[8] = {false};
+  if (!attr_done[c->device & 7]) {
+    cudaError_t e = cudaFuncSetAttribute(cm_ln_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)CMLN_SMEM);
+    if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "channel LayerNorm smem attribute: %s", cudaGetErrorString(e));
+    attr_done[c->device & 7] = true;
+  }
+  cm_ln_kernel<<<(int)blocks, 256, CMLN_SMEM, st>>>(in, chan_stride, row_stride, R, N, out, gamma, beta, eps);
   return check_launch(c, "cm_ln_kernel");
 }
 
