@@ -89,7 +89,8 @@ def _gloo_trimul_worker(rank, world, port, ref_src, n, seed, outgoing, ret):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("XFOLD_REFERENCE"), required="XFOLD_REFERENCE" not in os.environ,
+                    help="checkout of the reference project (the directory that holds src/distributed_xfold)")
     ap.add_argument("--write", action="store_true")
     args = ap.parse_args()
     ref_src = os.path.join(args.reference, "src")
