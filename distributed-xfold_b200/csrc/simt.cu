@@ -170,17 +170,18 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
              const float* __restrict__ pw, float* __restrict__ proj, long long proj_plane,
              const bf16* __restrict__ mod_scale, const bf16* __restrict__ mod_shift, int mod_rows,
              bf16* __restrict__ proj_bf16, int trav_inner, int trav_outer, int proj_pitch) {
-  constexpr int SLOTS = (H == 0) ? 4 : (H == 4 ? 2 : 1);
-  extern __shared__ float s_pw[];  // H x 128 projection weights
+  // dynamic shared memory: H x 128 projection weights, then two tiles of 128 rows x 256 B.  The tile of the next
+  // iteration is fetched with cp.async while the current one is processed, so loads stay in flight all the time.
+  extern __shared__ __align__(16) float s_pw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>(s_pw + H * 128);
   if constexpr (H > 0) {
     // stored as [head][half][lane16][4] so that the 16 lanes of a row read consecutive 16-byte words
     for (int i = threadIdx.x; i < H * 128; i += blockDim.x) {
       const int h = i >> 7, c = i & 127;
       s_pw[((h * 2 + ((c >> 2) & 1)) * 16 + (c >> 3)) * 4 + (c & 3)] = pw[i];
     }
-    __syncthreads();
   }
-  const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15;
+  const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15, warp = threadIdx.x >> 5;
   const int c0 = l16 * 8;
   float gm[8], bt[8];
 #pragma unroll
@@ -188,25 +189,37 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
     gm[e] = gamma ? gamma[c0 + e] : 1.f;
     bt[e] = beta ? beta[c0 + e] : 0.f;
   }
-  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
-  for (long long base = warp_global * 2; base < rows; base += nwarps * 2 * SLOTS) {
-    uint4 raw[SLOTS];
-    long long srow[SLOTS], pidx[SLOTS];
-    bool valid[SLOTS];
-#pragma unroll
-    for (int j = 0; j < SLOTS; ++j) {
-      const long long prow = base + (long long)j * nwarps * 2 + half;
-      valid[j] = prow < rows;
-      const long long inner = trav_inner > 0 ? trav_inner : -trav_inner;
-      srow[j] = trav_inner > 0 ? (prow % inner) * trav_outer + prow / inner : prow;
-      pidx[j] = trav_inner != 0 ? (prow / inner) * proj_pitch + prow % inner : prow;
-      raw[j] = make_uint4(0, 0, 0, 0);
-      if (valid[j]) raw[j] = *reinterpret_cast<const uint4*>(x + srow[j] * ldx + c0);
+  // transposed traversal: projection index (y, x) = (prow / inner, prow % inner) reads source row x * outer + y
+  // trav_inner < 0: plain walk, but the projection rows (of -trav_inner entries) have pitch proj_pitch
+  const long long inner = trav_inner > 0 ? trav_inner : -trav_inner;
+  auto srow_of = [&](long long prow) { return trav_inner > 0 ? (prow % inner) * trav_outer + prow / inner : prow; };
+  auto pidx_of = [&](long long prow) { return trav_inner != 0 ? (prow / inner) * proj_pitch + prow % inner : prow; };
+  const long long ntiles = (rows + 127) / 128;
+  auto fetch = [&](long long t, int buf) {
+    for (int idx = threadIdx.x; idx < 128 * 16; idx += 256) {
+      const long long prow = t * 128 + (idx >> 4);
+      if (prow < rows)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                     ::"r"(smem_u32(tiles + buf * 32768 + idx * 16)), "l"(x + srow_of(prow) * ldx + (idx & 15) * 8) : "memory");
     }
-#pragma unroll
-    for (int j = 0; j < SLOTS; ++j) {
-      const uint32_t w4[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  int buf = 0;
+  if ((long long)blockIdx.x < ntiles) fetch(blockIdx.x, 0);
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, buf ^= 1) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // tile t is complete; every thread is done with the other buffer (and s_pw is filled)
+    if (t + gridDim.x < ntiles) fetch(t + gridDim.x, buf ^ 1);
+    constexpr int UNR = (H >= 16) ? 1 : 2;  // the wide projections hold 16 accumulators per row
+#pragma unroll UNR
+    for (int it = 0; it < 8; ++it) {
+      const int r = warp * 16 + it * 2 + half;
+      const long long prow_j = t * 128 + r;
+      const bool valid_j = prow_j < rows;
+      const long long srow_j = srow_of(prow_j);
+      uint4 rawv = make_uint4(0, 0, 0, 0);
+      if (valid_j) rawv = *reinterpret_cast<const uint4*>(tiles + buf * 32768 + r * 256 + l16 * 16);
+      const uint32_t w4[4] = {rawv.x, rawv.y, rawv.z, rawv.w};
       float v[8];
       float s = 0.f;
 #pragma unroll
@@ -229,8 +242,8 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
       const float rstd = rsqrtf(ss * (1.f / 128) + eps);
 #pragma unroll
       for (int e = 0; e < 8; ++e) v[e] = fmaf(v[e] * rstd, gm[e], bt[e]);
-      if (mod_scale && valid[j]) {
-        const long long mr = srow[j] % mod_rows;
+      if (mod_scale && valid_j) {
+        const long long mr = srow_j % mod_rows;
         const uint4 a = *reinterpret_cast<const uint4*>(mod_scale + mr * 128 + c0);
         const uint4 b = *reinterpret_cast<const uint4*>(mod_shift + mr * 128 + c0);
         const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
@@ -240,11 +253,11 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
           v[2 * e + 1] = sigmoidf_fast(bf16_hi(aw[e])) * v[2 * e + 1] + bf16_hi(bw[e]);
         }
       }
-      if (y && valid[j]) {
+      if (y && valid_j) {
         uint4 u;
         u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
         u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(y + srow[j] * ldy + c0) = u;
+        *reinterpret_cast<uint4*>(y + srow_j * ldy + c0) = u;
       }
       if constexpr (H > 0) {
 #pragma unroll
@@ -281,8 +294,8 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
           const int hsel = (G == 16) ? (((l16 >> 3) & 1) * 8 + ((l16 >> 2) & 1) * 4 + ((l16 >> 1) & 1) * 2 + (l16 & 1))
                                      : (((l16 >> 3) & 1) * 2 + ((l16 >> 2) & 1));
           const bool writer = (G == 16) ? true : ((l16 & 3) == 0);
-          if (writer && valid[j]) {
-            const long long o = (long long)(hb + hsel) * proj_plane + pidx[j];
+          if (writer && valid_j) {
+            const long long o = (long long)(hb + hsel) * proj_plane + pidx_of(prow_j);
             if (proj_bf16) proj_bf16[o] = __float2bfloat16(acc[0] * kBiasLog2e);
             else proj[o] = acc[0];
           }
@@ -290,6 +303,7 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
 static int launch_ln128(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, const float* g,
@@ -297,12 +311,27 @@ static int launch_ln128(Ctx* c, const bf16* x, long long ldx, bf16* y, long long
                         const bf16* msc, const bf16* msh, int mod_rows, bf16* pbf, int tin, int tout, int tpitch,
                         cudaStream_t st) {
   if ((ldx & 7) || (ldy & 7)) return fail(c, XFOLD_ERR_ARG, "layernorm(128): row strides must be multiples of 8 elements");
-  const int slots = (H == 0) ? 4 : (H == 4 ? 2 : 1);
-  long long blocks = (rows + 16 * slots - 1) / (16 * slots);  // 8 warps x 2 rows x slots per pass
-  const long long cap = (long long)c->sm_count * 3;  // one wave of resident CTAs (3 per SM): the loop is grid-strided
+  long long blocks = (rows + 127) / 128;  // tiles of 128 rows
+  const long long cap = (long long)c->sm_count * (H <= 16 ? 3 : 2);  // one wave of resident CTAs: the loop is grid-strided
   if (blocks > cap) blocks = cap;
   if (blocks <= 0) return XFOLD_OK;
-  const size_t sm = (size_t)H * 128 * sizeof(float);
+  const size_t sm = (size_t)H * 128 * sizeof(float) + 2 * 32768;
+  {
+    static bool attr_done[8][4] = {};
+    const int hi = H == 0 ? 0 : H == 4 ? 1 : H == 16 ? 2 : 3;
+    if (!attr_done[c->device & 7][hi]) {
+      cudaError_t e = cudaSuccess;
+      switch (H) {
+        case 0: e = cudaFuncSetAttribute(ln128_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); break;
+        case 4: e = cudaFuncSetAttribute(ln128_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); break;
+        case 16: e = cudaFuncSetAttribute(ln128_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); break;
+        case 64: e = cudaFuncSetAttribute(ln128_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm); break;
+        default: break;
+      }
+      if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "layernorm smem attribute: %s", cudaGetErrorString(e));
+      attr_done[c->device & 7][hi] = true;
+    }
+  }
   ProfScope ps(c, XFOLD_K_LAYERNORM, st);
   switch (H) {
     case 0: ln128_kernel<0><<<(int)blocks, 256, sm, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, proj, plane, msc, msh, mod_rows, pbf, tin, tout, tpitch); break;
