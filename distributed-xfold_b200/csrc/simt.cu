@@ -220,23 +220,26 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
       uint4 rawv = make_uint4(0, 0, 0, 0);
       if (valid_j) rawv = *reinterpret_cast<const uint4*>(tiles + buf * 32768 + r * 256 + l16 * 16);
       const uint32_t w4[4] = {rawv.x, rawv.y, rawv.z, rawv.w};
+      // The kernel is bound by instruction issue, so the bf16 values are never unpacked: mixed-precision adds take the
+      // packed halves as they are, once for the row sum and once to produce the centred fp32 values.
       float v[8];
-      float s = 0.f;
+      float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        v[2 * e] = bf16_lo(w4[e]);
-        v[2 * e + 1] = bf16_hi(w4[e]);
-        s += v[2 * e] + v[2 * e + 1];
-      }
+      for (int e = 0; e < 4; ++e)
+        asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+            : "+f"(s0), "+f"(s1) : "r"(w4[e]));
+      float s = s0 + s1;
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
       const float mean = s * (1.f / 128);
+      const float nmean = -mean;
       float ss = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        v[e] -= mean;
-        ss += v[e] * v[e];
-      }
+      for (int e = 0; e < 4; ++e)
+        asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %3;\n\tadd.rn.f32.bf16 %1, hi, %3;\n\t}"
+            : "=f"(v[2 * e]), "=f"(v[2 * e + 1]) : "r"(w4[e]), "f"(nmean));
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       const float rstd = rsqrtf(ss * (1.f / 128) + eps);
