@@ -309,11 +309,245 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// LayerNorm of 128-wide rows with the 4- or 16-head pair-bias projection on the tensor core.
+//
+// The projection on the CUDA cores costs 32 (4 heads) or 128 (16 heads) FMAs per lane and row and made those launches
+// 2x / 4.5x as long as the plain LayerNorm.  Here the tile of 128 RAW rows that cp.async stages in shared memory is
+// laid out as the K-major, 128-byte-swizzled A operand of tcgen05.mma, and one 128 x 16 x 128 product per tile
+//     D[row][h] = sum_c x[row][c] * w'[h][c],      w'[h][c] = bf16(w[h][c] * gamma[c])
+// gives the un-normalised dot products; the LayerNorm enters through the row statistics the warps compute anyway:
+//     proj[h][row] = rstd * (D - mean * colsum[h]) + colbias[h],  colsum[h] = sum_c w'[h][c],  colbias[h] = sum_c beta[c] w[h][c]
+// (colsum from the rounded w', so a constant row cancels exactly).  The output is the attention kernel's bf16
+// operand (times log2 e); y (the normalised rows) is written when asked for.
+// ---------------------------------------------------------------------------------------------
+constexpr uint32_t LNTC_TILE = 32768;  // 128 rows x 256 B: two swizzled halves of 64 channels
+constexpr uint32_t LNTC_OFF_W = 2 * LNTC_TILE, LNTC_OFF_MISC = LNTC_OFF_W + 4096;
+constexpr uint32_t LNTC_SMEM = LNTC_OFF_MISC + 2048 + 1024;
+
+template <int H>
+__global__ void __launch_bounds__(256, 3)
+ln128_tc_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, long long ldy, long long rows,
+                const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                const float* __restrict__ pw, long long proj_plane, bf16* __restrict__ proj_bf16, int trav_inner,
+                int trav_outer, int proj_pitch, int* status) {
+  extern __shared__ uint8_t lntc_raw[];
+  const uint32_t raw_addr = smem_u32(lntc_raw);
+  uint8_t* smem = lntc_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sW = smem + LNTC_OFF_W;                                     // [2 halves][16 heads][128 B], swizzled
+  float* colsum = reinterpret_cast<float*>(smem + LNTC_OFF_MISC);      // [16]
+  float* colbias = colsum + 16;                                        // [16]
+  float2* rstat = reinterpret_cast<float2*>(smem + LNTC_OFF_MISC + 128);  // [128] (mean, rstd) of the tile's rows
+  uint64_t* mma_bar = reinterpret_cast<uint64_t*>(smem + LNTC_OFF_MISC + 128 + 1024);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(mma_bar + 1);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int lane = threadIdx.x & 31, half = lane >> 4, l16 = lane & 15, warp = threadIdx.x >> 5;
+  const AbortCtx ab{cta_abort, status};
+
+  // folded weights: one head per half-warp pass
+  for (int h = warp * 2 + half; h < 16; h += 16) {
+    float s = 0.f, b = 0.f;
+    uint32_t packed[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float w2[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int c = l16 * 8 + e * 2 + u;
+        const float w = h < H ? pw[h * 128 + c] : 0.f;
+        const bf16 wf = __float2bfloat16(w * (gamma ? gamma[c] : 1.f));
+        w2[u] = __bfloat162float(wf);
+        s += w2[u];
+        b += (beta ? beta[c] : 0.f) * w;
+      }
+      packed[e] = pack_bf16x2(w2[0], w2[1]);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      s += __shfl_xor_sync(0xffffffffu, s, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    // channels l16*8 .. +7 = 16-byte chunk (l16 & 7) of half (l16 >> 3) in row h
+    *reinterpret_cast<uint4*>(sW + (l16 >> 3) * 2048 + h * 128 + ((uint32_t(l16 & 7) ^ uint32_t(h & 7)) << 4)) =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    if (l16 == 0) {
+      colsum[h] = s;
+      colbias[h] = b;
+    }
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(mma_bar, 1);
+    *cta_abort = 0;
+    fence_barrier_init();
+  }
+  fence_proxy_async_smem();
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int c0 = l16 * 8;
+  float gm[8], bt[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    gm[e] = gamma ? gamma[c0 + e] : 1.f;
+    bt[e] = beta ? beta[c0 + e] : 0.f;
+  }
+  const long long inner = trav_inner > 0 ? trav_inner : -trav_inner;
+  auto srow_of = [&](long long prow) { return trav_inner > 0 ? (prow % inner) * trav_outer + prow / inner : prow; };
+  auto pidx_of = [&](long long prow) { return trav_inner != 0 ? (prow / inner) * proj_pitch + prow % inner : prow; };
+  const long long ntiles = (rows + 127) / 128;
+  // 16-byte piece w (0..15) of row r: half w >> 3, chunk (w & 7) ^ (r & 7) of the 128-byte swizzled row
+  auto piece = [&](int buf, int r, int w) {
+    return smem + buf * LNTC_TILE + (w >> 3) * 16384 + r * 128 + ((uint32_t(w & 7) ^ uint32_t(r & 7)) << 4);
+  };
+  auto fetch = [&](long long t, int buf) {
+    for (int idx = threadIdx.x; idx < 128 * 16; idx += 256) {
+      const int r = idx >> 4, w = idx & 15;
+      const long long prow = t * 128 + r;
+      if (prow < rows)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                     ::"r"(smem_u32(piece(buf, r, w))), "l"(x + srow_of(prow) * ldx + w * 8) : "memory");
+      else
+        *reinterpret_cast<uint4*>(piece(buf, r, w)) = make_uint4(0, 0, 0, 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  constexpr uint32_t idesc = make_idesc(128, 16);
+  constexpr float kLog2e = 1.4426950408889634f;
+  int buf = 0;
+  uint32_t iter = 0;
+  if ((long long)blockIdx.x < ntiles) fetch(blockIdx.x, 0);
+  for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, buf ^= 1, ++iter) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    fence_proxy_async_smem();  // the tile was written through the generic proxy; the tensor core reads it through the async one
+    __syncthreads();           // tile t complete; all reads of the accumulator and of the other buffer are over
+    if (threadIdx.x == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int hf = 0; hf < 2; ++hf) {
+        const uint64_t ad = make_sdesc(smem_u32(smem + buf * LNTC_TILE + hf * 16384), 16, 1024);
+        const uint64_t bd = make_sdesc(smem_u32(sW + hf * 2048), 16, 1024);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_ss(tmem_base, ad + 2 * k, bd + 2 * k, idesc, (hf | k) ? 1u : 0u);
+      }
+      umma_commit(mma_bar);
+    }
+    if (t + gridDim.x < ntiles) fetch(t + gridDim.x, buf ^ 1);
+    // row statistics (and the normalised rows, when asked for) while the product runs
+    constexpr int UNR = 2;
+#pragma unroll UNR
+    for (int it = 0; it < 8; ++it) {
+      const int r = warp * 16 + it * 2 + half;
+      const long long prow = t * 128 + r;
+      const bool valid = prow < rows;
+      const uint4 rawv = *reinterpret_cast<const uint4*>(piece(buf, r, l16));
+      const uint32_t w4[4] = {rawv.x, rawv.y, rawv.z, rawv.w};
+      float v[8];
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %1, hi, %1;\n\t}"
+            : "+f"(s0), "+f"(s1) : "r"(w4[e]));
+      float sm = s0 + s1;
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, o);
+      const float mean = sm * (1.f / 128);
+      const float nmean = -mean;
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.bf16 %0, lo, %3;\n\tadd.rn.f32.bf16 %1, hi, %3;\n\t}"
+            : "=f"(v[2 * e]), "=f"(v[2 * e + 1]) : "r"(w4[e]), "f"(nmean));
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rstd = rsqrtf(ss * (1.f / 128) + eps);
+      if (l16 == 0) rstat[r] = make_float2(mean, rstd);
+      if (y && valid) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = fmaf(v[e] * rstd, gm[e], bt[e]);
+        uint4 u;
+        u.x = pack_bf16x2(v[0], v[1]); u.y = pack_bf16x2(v[2], v[3]);
+        u.z = pack_bf16x2(v[4], v[5]); u.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(y + srow_of(prow) * ldy + c0) = u;
+      }
+    }
+    __syncthreads();  // statistics of all 128 rows are in shared memory
+    const bool okay = mbar_wait(mma_bar, iter & 1u, ab, XF_ERR_WAIT_TMEM_FULL);
+    if (okay) {
+      tc_fence_after();
+      // warp w reads TMEM lanes 32 * (w & 3) ..: row = that lane; warps 0-3 take heads 0-7, warps 4-7 heads 8-15
+      const int q = warp & 3, hsel = warp >> 2;
+      if (hsel * 8 < H) {
+        uint32_t d[8];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7])
+                     : "r"(tmem_base + hsel * 8 + (uint32_t(q * 32) << 16))
+                     : "memory");
+        tmem_ld_wait();
+        const int row = q * 32 + lane;
+        const long long prow = t * 128 + row;
+        if (prow < rows) {
+          const float2 st = rstat[row];
+          const long long o = pidx_of(prow);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int h = hsel * 8 + j;
+            if (h < H) {
+              const float val = fmaf(st.y, __uint_as_float(d[j]) - st.x * colsum[h], colbias[h]);
+              proj_bf16[(long long)h * proj_plane + o] = __float2bfloat16(val * kLog2e);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+    }
+    if (__syncthreads_or(!okay)) break;  // a bounded wait ran out: every thread leaves together
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+
+template <int H>
+static int launch_ln128_tc(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, const float* g,
+                           const float* b, float eps, const float* pw, long long plane, bf16* pbf, int tin, int tout,
+                           int tpitch, cudaStream_t st) {
+  long long blocks = (rows + 127) / 128;
+  const long long cap = (long long)c->sm_count * 3;
+  if (blocks > cap) blocks = cap;
+  if (blocks <= 0) return XFOLD_OK;
+  static bool attr_done[8] = {false};
+  if (!attr_done[c->device & 7]) {
+    cudaError_t e = cudaFuncSetAttribute(ln128_tc_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)LNTC_SMEM);
+    if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "layernorm smem attribute: %s", cudaGetErrorString(e));
+    attr_done[c->device & 7] = true;
+  }
+  ProfScope ps(c, XFOLD_K_LAYERNORM, st);
+  ln128_tc_kernel<H><<<(int)blocks, 256, LNTC_SMEM, st>>>(x, ldx, y, ldy, rows, g, b, eps, pw, plane, pbf, tin, tout, tpitch,
+                                                          c->d_status);
+  return check_launch(c, "ln128_tc_kernel");
+}
+
 static int launch_ln128(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, const float* g,
                         const float* b, float eps, int H, const float* pw, float* proj, long long plane,
                         const bf16* msc, const bf16* msh, int mod_rows, bf16* pbf, int tin, int tout, int tpitch,
                         cudaStream_t st) {
   if ((ldx & 7) || (ldy & 7)) return fail(c, XFOLD_ERR_ARG, "layernorm(128): row strides must be multiples of 8 elements");
+  if ((H == 4 || H == 16) && pbf && !proj && !msc) {  // the attention pair-bias operand: projection on the tensor core
+    if (H == 4) return launch_ln128_tc<4>(c, x, ldx, y, ldy, rows, g, b, eps, pw, plane, pbf, tin, tout, tpitch, st);
+    return launch_ln128_tc<16>(c, x, ldx, y, ldy, rows, g, b, eps, pw, plane, pbf, tin, tout, tpitch, st);
+  }
   long long blocks = (rows + 127) / 128;  // tiles of 128 rows
   const long long cap = (long long)c->sm_count * (H <= 16 ? 3 : 2);  // one wave of resident CTAs: the loop is grid-strided
   if (blocks > cap) blocks = cap;
