@@ -191,6 +191,25 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int tm = int((t / p.tiles_n) % p.tiles_m);
       const int b = int(t / ((long long)p.tiles_n * p.tiles_m));
       const uint32_t buf = it & 1u, aphase = (it >> 1) & 1u;
+      // TRIMUL_AB: where this thread's token goes, and its mask value, fetched BEFORE the wait for the accumulator so
+      // that the load's latency hides behind the product instead of heading every tile's epilogue
+      long long tok = 0, cm_off = 0;
+      bool rvalid = false;
+      float mk = 1.f;
+      if constexpr (EPI == EPI_TRIMUL_AB) {
+        if (p.a_row_mode == 0) {
+          tok = (long long)tm * BM + row;
+          rvalid = tok < p.M;
+          const long long i = tok / p.ntok, j = tok - i * p.ntok;
+          cm_off = i * p.cm_ld + j;
+        } else {
+          const long long jf = tm % p.a_dim1, i = (long long)(tm / p.a_dim1) * BM + row;
+          rvalid = i * p.ntok < p.M;  // M = rows * ntok
+          tok = i * p.ntok + jf;
+          cm_off = jf * p.cm_ld + i;
+        }
+        if (tn < 2 && rvalid && p.mask) mk = p.mask[tok];
+      }
       if (!mbar_wait(&tfull[buf], aphase, ab, XF_ERR_WAIT_TMEM_FULL)) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + buf * BN + (uint32_t(q * 32) << 16);
@@ -347,21 +366,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       } else {  // EPI_TRIMUL_AB
         // tile_n 0: [projection | gate] rows of a; 1: the same for b; 2: gating_linear (first 128 columns)
-        long long tok, cm_off;
-        bool rvalid;
-        if (p.a_row_mode == 0) {
-          tok = (long long)tm * BM + row;
-          rvalid = tok < p.M;
-          const long long i = tok / p.ntok, j = tok - i * p.ntok;
-          cm_off = i * p.cm_ld + j;
-        } else {
-          const long long jf = tm % p.a_dim1, i = (long long)(tm / p.a_dim1) * BM + row;
-          rvalid = i * p.ntok < p.M;  // M = rows * ntok
-          tok = i * p.ntok + jf;
-          cm_off = jf * p.cm_ld + i;
-        }
         if (tn < 2) {
-          const float mk = (rvalid && p.mask) ? p.mask[tok] : 1.f;
           bf16* dst = (tn == 0 ? p.out_a : p.out_b) + cm_off;
 #pragma unroll 1
           for (int cc = ch * 2; cc < ch * 2 + 2; ++cc) {
