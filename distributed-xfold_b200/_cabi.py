@@ -80,6 +80,7 @@ SIGNATURES = {
     "xfold_transpose_scatter_fwd": (ci, [vp, vp, ci, ci, ci, C.POINTER(vp), C.POINTER(ci), ci, vp]),
     "xfold_trimul_scatter_channels_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, C.POINTER(vp), C.POINTER(vp), ci, vp]),
     "xfold_trimul_scatter_rows_fwd": (ci, [vp, vp, ci, ci, ci, ci, C.POINTER(vp), C.POINTER(ci), ci, vp]),
+    "xfold_peer_allgather_fwd": (ci, [vp, vp, ll, ll, C.POINTER(vp), ci, vp]),
     "xfold_peer_barrier": (ci, [vp, C.POINTER(vp), ci, ci, ci, vp]),
     "xfold_transition_static_max_bytes": (sz, []),
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),

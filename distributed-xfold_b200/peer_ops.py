@@ -50,3 +50,14 @@ def scatter_rows(o: torch.Tensor, chan0: int, peer_o: List[int], row_starts: Lis
     rc = load().xfold_trimul_scatter_rows_fwd(ctx(dev), o.data_ptr(), o.shape[0], chan0, o.shape[1], o.shape[2], po, starts,
                                               world, torch.cuda.current_stream(dev).cuda_stream)
     check(rc, dev, "xfold_trimul_scatter_rows_fwd")
+
+
+def peer_allgather(src: torch.Tensor, offset_bytes: int, peer_dst: List[int]) -> None:
+    """Copies this rank's contiguous block to byte offset ``offset_bytes`` of every rank's destination buffer."""
+    assert src.is_cuda and src.is_contiguous()
+    dev = src.device.index
+    world = len(peer_dst)
+    pd = (C.c_void_p * world)(*peer_dst)
+    rc = load().xfold_peer_allgather_fwd(ctx(dev), src.data_ptr(), src.numel() * src.element_size(), offset_bytes, pd, world,
+                                         torch.cuda.current_stream(dev).cuda_stream)
+    check(rc, dev, "xfold_peer_allgather_fwd")

@@ -66,6 +66,9 @@ class RowSharding:
         """[R_me, ...] on every rank -> [N, ...] (ragged row counts allowed)."""
         if self.world == 1:
             return local
+        peer = getattr(self, "peer", None)
+        if peer is not None and local.is_cuda and local.dtype == torch.bfloat16 and local.numel() * 2 >= peer.GATHER_MIN_BYTES:
+            return peer.gather_rows(local)
         out = local.new_empty((self.n,) + tuple(local.shape[1:]))
         if len(set(self.sizes)) == 1:
             dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
@@ -190,6 +193,32 @@ class PeerExchange:
         self.k = k ^ 1
         return self.bufs[k][: sh.r * sh.n * self.c].view(sh.r, sh.n, self.c)
 
+
+    # -- all-gather of large row blocks (the b operand at 2 ranks) by peer stores ----------------------
+    # Only the b operand of the TriangleMultiplication is this large.  Its buffer is rewritten by the peers at the next
+    # TriangleMultiplication, and a distributed transpose (with its barrier) always lies between two of them, so every
+    # rank has finished reading before anyone writes again.  Smaller gathers (pair bias, pair logits) have no such
+    # barrier before the buffer's next use and stay with the library collective.
+    GATHER_MIN_BYTES = 32 << 20
+
+    def gather_rows(self, local: torch.Tensor) -> torch.Tensor:
+        sh = self.sh
+        local = local.contiguous()
+        row_bytes = local[0].numel() * 2
+        if row_bytes % 16 or local.data_ptr() % 16:
+            raise ValueError("peer gather needs 16-byte aligned rows")
+        total = sh.n * row_bytes
+        g = getattr(self, "gbuf", None)
+        if g is None or g["bytes"] < total:
+            t = self.symm.empty(total // 2, dtype=torch.bfloat16, device=local.device)
+            h = self.symm.rendezvous(t, self.group)
+            off = t.data_ptr() - int(h.buffer_ptrs[sh.rank])
+            torch.cuda.synchronize(local.device)
+            dist.barrier(group=sh.group)
+            g = self.gbuf = {"bytes": total, "t": t, "ptrs": [int(p) + off for p in h.buffer_ptrs]}
+        self.ops.peer_allgather(local, sh.rows.start * row_bytes, g["ptrs"])
+        self._barrier(local.device)
+        return g["t"][: total // 2].view((sh.n,) + tuple(local.shape[1:]))
 
     # -- channel-sharded contraction: operand planes and output rows in peer-mapped buffers ------------
     def _plane_buffers(self, ld: int, ldo: int, device):

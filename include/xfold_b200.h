@@ -262,6 +262,11 @@ int xfold_trimul_scatter_channels_fwd(xfold_ctx* ctx, const void* a, const void*
  * (i - row_starts[p], chan0 + c): the layout xfold_trimul_output_fwd reads. */
 int xfold_trimul_scatter_rows_fwd(xfold_ctx* ctx, const void* o, int channels, int chan0, int N, int ldo,
                                   void* const* peer_o, const int* row_starts, int world, void* stream);
+/* All-gather by peer stores (in place of distribute_utils.py:219-262 for a contiguous block per rank): this rank's
+ * block of `bytes` bytes is copied to byte offset `offset_bytes` of every rank's destination buffer (peer_dst[q],
+ * mapped into this process).  Sizes, offsets and the source are multiples of 16 bytes.  Follow with xfold_peer_barrier. */
+int xfold_peer_allgather_fwd(xfold_ctx* ctx, const void* src, long long bytes, long long offset_bytes,
+                             void* const* peer_dst, int world, void* stream);
 /* Flag barrier between the ranks (the reference uses dist.barrier, run_inference.py:154-245): rank `me`
  * stores `epoch` into slot `me` of every rank's flag array (peer_flags[q], 8 ints, zero-initialised) and
  * waits until all slots of its own array reached `epoch`.  The wait is bounded; a time-out is reported by
