@@ -86,6 +86,7 @@ SIGNATURES = {
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),
     "xfold_pairformer_workspace_bytes": (sz, [ci]),
     "xfold_pairformer_block_fwd": (ci, [vp, vp, vp, vp, vp, ci, C.POINTER(PairformerWeights), vp, sz, vp]),
+    "xfold_pairformer_stack_fwd": (ci, [vp, vp, vp, vp, vp, ci, C.POINTER(PairformerWeights), ci, vp, sz, vp]),
 }
 
 _lib: Optional[C.CDLL] = None

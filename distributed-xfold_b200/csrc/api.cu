@@ -357,6 +357,8 @@ static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const x
                           size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr) {
   if (!x || !w || !w->w1_packed || !w->w2) return fail(c, XFOLD_ERR_ARG, "transition: null argument");
   if (rows <= 0) return XFOLD_OK;
+  // before any size arithmetic or launch: row counts the kernels cannot index, or whose byte sizes would wrap
+  if (C <= 0 || F <= 0 || rows >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "transition: bad shape (%lld rows, C=%d, F=%d)", rows, C, F);
   Carver cv(ws, ws_bytes);
   bf16* xn = (bf16*)cv.take((size_t)rows * C * 2);
   bf16* h = (bf16*)cv.take((size_t)rows * F * 2);
@@ -389,9 +391,21 @@ static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
 }
 
 // pair_bias: float32 [H][S][S], or, when pair_biasT is given, the same as bf16 [H][S][pad8(S)] (both [h][query][key])
+static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
+                         const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
+                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st);
 static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
                         const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+  c->attn_tag = XFOLD_K_APB_ATTENTION;  // accounted separately from the TriangleAttention launches
+  const int rc = apb_core_fwd_(c, xn, B, S, C, H, Dp, w_qkvg, qkvg_bias, qkvg_scale, pair_bias, pair_biasT, mask, out, ws,
+                               ws_bytes, st);
+  c->attn_tag = XFOLD_K_ATTENTION;
+  return rc;
+}
+static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
+                         const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
+                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (!xn || !w_qkvg || !out || (!pair_bias && !pair_biasT)) return fail(c, XFOLD_ERR_ARG, "apb: null argument");
   if ((Dp != 32 && Dp != 64) || (H * Dp) % 128) return fail(c, XFOLD_ERR_ARG, "apb: H x Dp must be a multiple of 128 with Dp 32 or 64");
   Carver cv(ws, ws_bytes);
@@ -641,6 +655,18 @@ int xfold_pairformer_block_fwd(xfold_ctx* c, void* z, void* s, const float* pair
   return pairformer_fwd(c, (bf16*)z, (bf16*)s, pair_mask, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
 }
 
+int xfold_pairformer_stack_fwd(xfold_ctx* c, void* z, void* s, const float* pair_mask, const float* seq_mask, int N,
+                               const xfold_pairformer_weights* blocks, int num_blocks, void* ws, size_t ws_bytes,
+                               void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  if (num_blocks < 0 || (num_blocks > 0 && !blocks)) return fail(c, XFOLD_ERR_ARG, "pairformer stack: no weights for %d blocks", num_blocks);
+  for (int i = 0; i < num_blocks; ++i) {
+    const int rc = pairformer_fwd(c, (bf16*)z, (bf16*)s, pair_mask, seq_mask, N, &blocks[i], ws, ws_bytes, (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  return XFOLD_OK;
+}
+
 /* ---- row-shard stages ------------------------------------------------------------------------ */
 int xfold_trimul_project_fwd(xfold_ctx* c, const void* z, const float* mask, int R, int N, const xfold_trimul_weights* w,
                              void* x_scratch, void* a, void* b, void* g, int ld, void* stream) {
@@ -731,7 +757,8 @@ size_t xfold_transition_static_max_bytes(void) { return XFOLD_STATIC_SCRATCH_BYT
 int xfold_transition_static_fwd(xfold_ctx* c, void* x, long long rows, int C, int F, const xfold_transition_weights* w,
                                 void* stream) {
   if (!c) return XFOLD_ERR_ARG;
-  if (rows < 0 || C <= 0 || F <= 0) return fail(c, XFOLD_ERR_ARG, "transition (static scratch): bad shape");
+  if (rows < 0 || C <= 0 || F <= 0 || rows >= (1ll << 31))
+    return fail(c, XFOLD_ERR_ARG, "transition (static scratch): bad shape (%lld rows, C=%d, F=%d)", rows, C, F);
   const size_t need = xfold_transition_workspace_bytes(rows, C, F);
   if (need > XFOLD_STATIC_SCRATCH_BYTES)
     return fail(c, XFOLD_ERR_ARG,

@@ -374,7 +374,7 @@ int launch_attention(Ctx* c, int D, const CUtensorMap& tm, const AttnArgs& a, in
   if (qt <= 0 || a.B <= 0 || head_groups <= 0) return XFOLD_OK;
   if (a.B > 65535 || head_groups > 65535) return fail(c, XFOLD_ERR_ARG, "attention: batch %d / head groups %d exceed the grid limit", a.B, head_groups);
   dim3 grid(qt, head_groups, a.B);
-  ProfScope ps(c, XFOLD_K_ATTENTION, st);
+  ProfScope ps(c, c->attn_tag, st);
   if (D == 32) {
     if (!attr_done[0][c->device & 7]) {
       cudaError_t e = cudaFuncSetAttribute(attn_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);

@@ -31,8 +31,6 @@
 // The pair bias arrives as bf16 [head][query][key], multiplied by log2(e) (key contiguous, row pitch a multiple of 8); TMA lays a
 // [128 queries][64 keys] tile out with the 128-byte swizzle, so the per-row 16-byte reads of the softmax
 // threads are bank-conflict free.
-#include <cstdlib>
-
 #include <cuda_fp16.h>
 
 #include "internal.h"
@@ -85,13 +83,6 @@ __device__ __forceinline__ void tmem_st32_(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-#ifdef A2_TIMELINE
-__device__ long long* g_a2_tl = nullptr;
-#define TL(role, ev) do { if (blockIdx.x == 0 && tl && tln < 4000) tl[(role) * 4096 + tln++] = (clock64() << 8) | (ev); } while (0)
-#else
-#define TL(role, ev) do {} while (0)
-#endif
-
 __global__ void __launch_bounds__(A2_THREADS, 1)
 attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmkv,
              const __grid_constant__ CUtensorMap tmb, const Attn2Args p) {
@@ -123,10 +114,6 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef A2_TIMELINE
-  long long* tl = (lane == 0) ? g_a2_tl : nullptr;
-  int tln = 0;
-#endif
   const AbortCtx ab{cta_abort, p.status};
   const int KB = (p.S + 63) / 64;
   // Persistent CTA: work items (batch row, head pair, query tile), batch row slowest so that the K / V rows of
@@ -196,13 +183,11 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         for (int kb = 0; kb < KB; ++kb, ++j) {
           const uint32_t st = uint32_t(j & (A2_KV - 1)), par = uint32_t((j / A2_KV) & 1) ^ 1u;
           if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-          TL(0, 1);
           mbar_arrive_expect_tx(&k_full[st], A2_H + 2048);
           if (p.transposed) tma_load_3d(sK + st * A2_H, &tmkv, &k_full[st], p.k_col0 + hp * 64, b, kb * 64);
           else tma_load_3d(sK + st * A2_H, &tmkv, &k_full[st], p.k_col0 + hp * 64, kb * 64, b);
           bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
           if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-          TL(0, 4);
           mbar_arrive_expect_tx(&v_full[st], A2_H);
           if (p.transposed) tma_load_3d(sV + st * A2_H, &tmkv, &v_full[st], p.v_col0 + hp * 64, b, kb * 64);
           else tma_load_3d(sV + st * A2_H, &tmkv, &v_full[st], p.v_col0 + hp * 64, kb * 64, b);
@@ -226,7 +211,6 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         const uint32_t s = aj & 1u, ks = aj & uint32_t(A2_KV - 1), kpar = (aj / A2_KV) & 1u;
         if (akb == 0 && !mbar_wait(&q_full[ait & 1], (ait >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
         if (!k_ready && !mbar_wait(&k_full[ks], kpar, ab, XF_ERR_WAIT_FULL)) return false;
-        if (w == 0) TL(1, 17);
         tc_fence_after();
         const uint32_t d = tmem_base + w * 128 + s * 64;
         const uint64_t qd = make_sdesc(smem_u32(sQ) + (ait & 1u) * A2_T + w * 64, 16, 1024);
@@ -257,10 +241,8 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
         const bool k_ready = aj < G && mbar_test_wait(&k_full[aj & uint32_t(A2_KV - 1)], (aj / A2_KV) & 1u);
         if (!mbar_wait(&p_ready[w * 2 + s], (g >> 1) & 1u, ab, XF_ERR_WAIT_ATTN)) break;
-        if (w == 0) TL(1, 14);
         // P(g) is published (and with it the logits buffer and bias tile of block g are free for block g + 2)
         if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
-        if (w == 0) TL(1, 15);
         tc_fence_after();
         const uint32_t pt = tmem_base + A2_TM_P + w * 64 + s * 32;
         const uint32_t vbase = smem_u32(sV) + vs * A2_H + w * 64;
@@ -273,9 +255,7 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         umma_commit(&pv_done[w * 2 + s]);
         umma_commit(&v_empty[vs]);
         if (++kb == KB) kb = 0;
-        if (w == 0) TL(1, 16);
         if (aj < G) okay = issue_ahead(k_ready);
-        if (w == 0) TL(1, 18);
       }
     }
   } else {
@@ -287,9 +267,6 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
     const uint32_t o_addr = tmem_base + A2_TM_O + w * 32 + lane_addr;
     const uint32_t p_addr = tmem_base + A2_TM_P + w * 64 + lane_addr;
     const uint32_t rsw = uint32_t(row & 7);
-#ifdef A2_TIMELINE
-    if (q4 != 2) tl = nullptr;
-#endif
     uint32_t g = 0;  // block number
     bool okay = true;
     bool ready = false;  // the probe of this block's barrier, made before the previous block's sweep, succeeded
@@ -306,14 +283,12 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         // One barrier covers the logits and the bias tile.  It also covers the P buffer: the issuer queued
         // S(g) behind the P V product of block g - 2, so P buffer s has been consumed when S(g) is complete.
         if (!ready && !mbar_wait(&sb_full[w * 2 + s], par, ab, XF_ERR_WAIT_ATTN)) { okay = false; break; }
-        TL(2 + w, 20);
         tc_fence_after();
         uint32_t r[64];
         tmem_ld32(s_addr + s * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
         tmem_ld32(s_addr + s * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
         ready = mbar_test_wait(&sb_full[w * 2 + (s ^ 1u)], uint32_t(((g + 1) >> 1) & 1));  // probe block g + 1
         tmem_ld_wait();
-        TL(2 + w, 22);
         bool exact = kb == 0;
         __half2 hs[4];
         uint32_t pk[32];
@@ -396,7 +371,6 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         l_run += ls0 + ls1;
         tmem_st32_(p_addr + s * 32, pk);
         tmem_st_wait_();
-        TL(2 + w, 27);
         tc_fence_before();
         mbar_arrive(&p_ready[w * 2 + s]);
       }
@@ -430,7 +404,6 @@ attn2_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           *reinterpret_cast<uint4*>(orow + g8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
       }
-      TL(2 + w, 28);
     }
   }
 
@@ -554,13 +527,7 @@ int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int tra
   const long long items = (long long)((S + 127) / 128) * (heads / 2) * B;
   if (items * ((S + 63) / 64) >= (1ll << 31)) return fail(c, XFOLD_ERR_ARG, "attention: batch x heads x sequence too large for one launch");
   const int grid = (int)(items < c->sm_count ? items : c->sm_count);
-#ifdef A2_TIMELINE
-  if (const char* e = getenv("XFOLD_ATTN_TL")) {
-    long long* ptr = (long long*)strtoull(e, nullptr, 16);
-    cudaMemcpyToSymbol(g_a2_tl, &ptr, sizeof(ptr));
-  }
-#endif
-  ProfScope ps(c, XFOLD_K_ATTENTION, st);
+  ProfScope ps(c, c->attn_tag, st);
   attn2_kernel<<<grid, A2_THREADS, A2_SMEM, st>>>(tmq, tmkv, tmb, a);
   return check_launch(c, "attn2_kernel");
 }

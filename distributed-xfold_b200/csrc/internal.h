@@ -25,6 +25,7 @@ struct Ctx {
   char last_error[256] = {0};
   long long launch_count = 0;  // kernels launched through this context
   int prof_on = 0;             // when set, every launch is bracketed by a pair of CUDA events
+  int attn_tag = XFOLD_K_ATTENTION;  // kernel class the attention launchers account their launch to
   std::vector<ProfRec> prof_recs, prof_pool;
 };
 

@@ -14,6 +14,18 @@
 //                       library all-gather it replaces, which was the largest part of the 2-GPU step's idle time).
 //   peer_barrier      : release / acquire flag barrier between the ranks.  The wait is bounded: when it runs
 //                       out the kernel records XF_ERR_WAIT_PEER in the status word and returns.
+//
+// Why two destination buffers are enough for the distributed transpose (the host alternates them, one per call):
+// call t stores into buffer k(t) of every rank and ends with flag barrier t.  What it produced is read, on rank p,
+// by the kernels between barrier t and p's own scatter kernel of call t + 1 (the pair representation lives in that
+// buffer and is updated in place; the scatter of call t + 1 is its last reader, after which the live copy is in the
+// other buffer).  Buffer k(t) is stored into again by call t + 2.  A rank q starts those stores only after it has
+// passed barrier t + 1, and it passes barrier t + 1 only after every rank p has published epoch t + 1, which p does
+// in stream order AFTER its scatter kernel of call t + 1.  Hence every read of buffer k(t) on every rank has
+// finished before any store of call t + 2 into it starts.  (Each flag store is a release at system scope after a
+// system-wide fence, each flag load an acquire, so the data stores of a call are visible before its flag.)  The same
+// argument covers the plane buffers of the channel-sharded contraction, which are written once per
+// TriangleMultiplication with a distributed transpose, i.e. a barrier, between two of them.
 #include "internal.h"
 #include "umma.cuh"
 

@@ -6,4 +6,4 @@ from .d_attention import DistributeGridSelfAttention  # noqa: F401
 from .d_primitives import DistributeTransition, Transition, LayerNorm  # noqa: F401
 from .d_diffusion_transformer import (AdaptiveLayerNorm, DistributeAdaLNZero, DistributeDiffusionTransition,  # noqa: F401
                                       DistributeSelfAttention, DistributeDiffusionTransformer)
-from .d_pairformer import DistributePairformerBlock  # noqa: F401
+from .d_pairformer import DistributePairformerBlock, DistributePairformerStack  # noqa: F401

@@ -354,6 +354,41 @@ def pairformer_block_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq
     return z, s
 
 
+class PackedPairformerStack:
+    """The blocks of a trunk (``trunk_pairformer.{i}.`` in the model's state dict, d_alphafold3.py:160-166) packed
+    into one contiguous array of weight structs, so that the whole loop is one C-ABI call."""
+
+    def __init__(self, blocks):
+        self.blocks = list(blocks)
+        self.c = (PairformerWeights * len(self.blocks))(*[b.c for b in self.blocks])
+
+    @classmethod
+    def from_state(cls, state: State, num_blocks: int, device, prefix: str = "trunk_pairformer.", with_single: bool = True):
+        return cls(PackedPairformerBlock(state, f"{prefix}{i}.", device, with_single) for i in range(num_blocks))
+
+    def __len__(self):
+        return len(self.blocks)
+
+    def __iter__(self):
+        return iter(self.blocks)
+
+
+def pairformer_stack_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq_mask, w: PackedPairformerStack):
+    """In place: the trunk loop of d_alphafold3.py:242-244, every block of ``w`` applied in order to z and s."""
+    _need_cuda(z, s, pair_mask, seq_mask)
+    assert z.dtype == BF16 and z.is_contiguous() and (s is None or (s.dtype == BF16 and s.is_contiguous()))
+    dev = _dev(z)
+    n = z.shape[0]
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_pairformer_workspace_bytes(n))
+    pm = None if pair_mask is None else pair_mask.to(torch.float32).contiguous()
+    sm = None if seq_mask is None else seq_mask.to(torch.float32).contiguous()
+    rc = lib.xfold_pairformer_stack_fwd(ctx(dev), _ptr(z), _ptr(s), _ptr(pm), _ptr(sm), n, w.c, len(w), _ptr(ws),
+                                        ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_pairformer_stack_fwd")
+    return z, s
+
+
 # ---------------------------------------------------------------------------------------------
 # row-shard stages (the multi-GPU block composes these with collectives in between)
 # ---------------------------------------------------------------------------------------------

@@ -23,6 +23,7 @@ gloo.  Nothing in this file computes on tensors itself except the layout glue.
 """
 from __future__ import annotations
 
+import math
 from typing import List, Optional
 
 import torch
@@ -51,10 +52,11 @@ def _exchange(send: List[torch.Tensor], recv: List[torch.Tensor], group) -> None
 class RowSharding:
     """Row partition of an N-token pair representation over a process group."""
 
-    def __init__(self, n_tokens: int, group=None):
+    def __init__(self, n_tokens: int, group=None, world: Optional[int] = None, rank: Optional[int] = None):
         self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        # world / rank may be given explicitly to work out a partition without a process group
+        self.world = world if world is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
         self.n = n_tokens
         info = ShardInfo(n_tokens, self.world)
         self.sizes, self.slices = info.shard_size_list, info.shard_slice_list
@@ -62,13 +64,25 @@ class RowSharding:
         self.r = self.sizes[self.rank]
 
     # -- collectives on shards -------------------------------------------------------------------
-    def gather_rows(self, local: torch.Tensor) -> torch.Tensor:
-        """[R_me, ...] on every rank -> [N, ...] (ragged row counts allowed)."""
+    # A gather smaller than this (in bytes of the GATHERED tensor) stays with the library collective.
+    PEER_GATHER_MIN_BYTES = 32 << 20
+
+    def uses_peer_gather(self, row_bytes: int, operand_b: bool) -> bool:
+        """Whether ``gather_rows`` takes the peer-store path.  Every rank must come to the same answer, or one side
+        would wait at the flag barrier while the other sits in a library collective: so the test uses only what
+        all ranks share -- the caller's statement that this is the b operand of the TriangleMultiplication, the
+        token count and the bytes per gathered row (never this rank's own row count, which differs on ragged
+        partitions)."""
+        return bool(operand_b) and getattr(self, "peer", None) is not None and self.n * row_bytes >= self.PEER_GATHER_MIN_BYTES
+
+    def gather_rows(self, local: torch.Tensor, operand_b: bool = False) -> torch.Tensor:
+        """[R_me, ...] on every rank -> [N, ...] (ragged row counts allowed).  ``operand_b``: the tensor is the b operand
+        of the TriangleMultiplication contraction, the one gather that may go through the peer-mapped buffer (see
+        ``PeerExchange.gather_rows`` for why only that one)."""
         if self.world == 1:
             return local
-        peer = getattr(self, "peer", None)
-        if peer is not None and local.is_cuda and local.dtype == torch.bfloat16 and local.numel() * 2 >= peer.GATHER_MIN_BYTES:
-            return peer.gather_rows(local)
+        if local.is_cuda and local.dtype == torch.bfloat16 and self.uses_peer_gather(2 * math.prod(local.shape[1:]), operand_b):
+            return self.peer.gather_rows(local)
         out = local.new_empty((self.n,) + tuple(local.shape[1:]))
         if len(set(self.sizes)) == 1:
             dist.all_gather_into_tensor(out, local.contiguous(), group=self.group)
@@ -153,7 +167,7 @@ class PeerExchange:
     """Distributed transpose through peer-mapped memory: each rank stores its tokens directly into the
     owning rank's buffer with one kernel (``xfold_transpose_scatter_fwd``), then the ranks meet at a bounded
     flag barrier (``xfold_peer_barrier``).  Two buffers alternate, so a buffer is rewritten only after the
-    barrier that follows its last read (see the ordering argument in the module docstring of the C source)."""
+    barrier that follows its last read (the ordering argument is written out in the header comment of csrc/peer.cu)."""
 
     def __init__(self, sh: "RowSharding", device, channels: int = 128):
         import torch.distributed._symmetric_memory as symm
@@ -194,12 +208,15 @@ class PeerExchange:
         return self.bufs[k][: sh.r * sh.n * self.c].view(sh.r, sh.n, self.c)
 
 
-    # -- all-gather of large row blocks (the b operand at 2 ranks) by peer stores ----------------------
-    # Only the b operand of the TriangleMultiplication is this large.  Its buffer is rewritten by the peers at the next
-    # TriangleMultiplication, and a distributed transpose (with its barrier) always lies between two of them, so every
-    # rank has finished reading before anyone writes again.  Smaller gathers (pair bias, pair logits) have no such
-    # barrier before the buffer's next use and stay with the library collective.
-    GATHER_MIN_BYTES = 32 << 20
+    # -- all-gather of the b operand of the TriangleMultiplication by peer stores ------------------------
+    # One buffer serves every such gather.  Ordering: the peers store into it at TriangleMultiplication t + 1 only
+    # after they passed the flag barrier of the distributed transpose that lies between TriangleMultiplication t and
+    # t + 1 in every block (and between the last one of a block and the first one of the next); a rank signals that
+    # barrier in stream order AFTER its contraction kernel of TriangleMultiplication t, the only reader of the
+    # buffer.  So every read of gather t has finished before any store of gather t + 1 starts.  No other gather has
+    # a barrier between its consumer and the next writer, which is why RowSharding.gather_rows sends only the
+    # b operand here (its callers say so explicitly; the size of a tensor never decides it) and the pair bias and
+    # pair logits stay with the library collective.
 
     def gather_rows(self, local: torch.Tensor) -> torch.Tensor:
         sh = self.sh
@@ -279,7 +296,7 @@ def _contract(sh: RowSharding, stages, a: torch.Tensor, b: torch.Tensor, n: int)
     if sh.channel_sharded:
         ap, bp = sh.rows_to_channels(a, b)
         return sh.channels_to_rows(stages.trimul_contract_planes(ap, bp, n))
-    return stages.trimul_contract(a, sh.gather_rows(b), n)
+    return stages.trimul_contract(a, sh.gather_rows(b, operand_b=True), n)
 
 
 def pairformer_block(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch.Tensor], pair_mask: torch.Tensor,
@@ -314,4 +331,25 @@ def pairformer_block(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch
         pl_loc = stages.pair_logits(z, w)                             # [16, R, ldq]
         pl = sh.gather_rows(pl_loc.transpose(0, 1).contiguous()).transpose(0, 1).contiguous()
         stages.single_update(s, pl, seq_mask, w)
+    return z, s
+
+
+def trimul_out_in(sh: RowSharding, stages, z: torch.Tensor, pair_mask: torch.Tensor, pair_mask_t: torch.Tensor,
+                  w_out, w_in) -> torch.Tensor:
+    """z += TriMul_outgoing(z); z += TriMul_incoming(z) on the row shard (nn/d_pairformer.py:122-123 with the sharded
+    form of nn/d_triangle_multiplication.py:48-99): the first two sub-layers of a block, also timed on their own."""
+    n, rows = sh.n, sh.rows
+    a, b, g = stages.trimul_project(z, pair_mask[rows], w_out)
+    stages.trimul_output(_contract(sh, stages, a, b, n), g, z, w_out)
+    zt = sh.transpose(z)
+    a, b, g = stages.trimul_project(zt, pair_mask_t[rows], w_in)
+    stages.trimul_output(_contract(sh, stages, a, b, n), g, zt, w_in)
+    return sh.transpose(zt)
+
+
+def pairformer_stack(sh: RowSharding, stages, z: torch.Tensor, s: Optional[torch.Tensor], pair_mask: torch.Tensor,
+                     pair_mask_t: torch.Tensor, seq_mask: Optional[torch.Tensor], blocks) -> tuple:
+    """The trunk loop (d_alphafold3.py:242-244) on the row shard: z stays sharded from the first block to the last."""
+    for w in blocks:
+        z, s = pairformer_block(sh, stages, z, s, pair_mask, pair_mask_t, seq_mask, w)
     return z, s

@@ -59,7 +59,8 @@ enum {
   XFOLD_K_MASK_BIAS = 8,
   XFOLD_K_SWIGLU = 9,
   XFOLD_K_PEER = 10,
-  XFOLD_K_COUNT = 11
+  XFOLD_K_APB_ATTENTION = 11, /* the attention kernel when launched for AttentionPairBias (XFOLD_K_ATTENTION: TriangleAttention) */
+  XFOLD_K_COUNT = 12
 };
 long long xfold_launch_count(xfold_ctx* ctx);
 int xfold_profile_enable(xfold_ctx* ctx, int on);
@@ -194,6 +195,13 @@ size_t xfold_pairformer_workspace_bytes(int N);
 int xfold_pairformer_block_fwd(xfold_ctx* ctx, void* z, void* s, const float* pair_mask, const float* seq_mask,
                                int N, const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream);
 
+/* The trunk loop `for pairformer_b in self.trunk_pairformer: pair, single = pairformer_b(...)`
+ * (d_alphafold3.py:242-244; the confidence head runs the same loop over its 4 blocks, :450-458): `num_blocks`
+ * blocks applied in order to the same z and s, `blocks` being an array of their weights. */
+int xfold_pairformer_stack_fwd(xfold_ctx* ctx, void* z, void* s, const float* pair_mask, const float* seq_mask, int N,
+                               const xfold_pairformer_weights* blocks, int num_blocks, void* ws, size_t ws_bytes,
+                               void* stream);
+
 /* ---- row-shard stages -------------------------------------------------------------------------
  * The pieces of TriangleMultiplication / TriangleAttention on a block of R pair rows, for the
  * multi-GPU block where the pair representation is partitioned by token rows
@@ -292,8 +300,8 @@ int xfold_transition_update_fwd(xfold_ctx* ctx, const void* x, void* update, lon
  * for hosts that are handed input/output buffers but may not call cudaMalloc themselves, e.g. a plugin
  * running inside another runtime's memory arena, or a latency path where allocation is forbidden.
  *  - Limit: xfold_transition_workspace_bytes(rows, C, F) must not exceed
- *    xfold_transition_static_max_bytes() (16 MiB: 4096 rows of the single representation, C 384 / F 1536,
- *    or 13107 pair tokens with C 128 / F 512); larger calls are rejected with XFOLD_ERR_ARG.
+ *    xfold_transition_static_max_bytes() (16 MiB: at most 4368 rows of the single representation, C 384 / F 1536,
+ *    or 13105 pair tokens with C 128 / F 512); larger calls are rejected with XFOLD_ERR_ARG.
  *  - Every GPU that loads the library carries the array until the process exits.
  *  - The first call on a device looks up the array's device address (the context's device must be
  *    current); make that first call before starting any stream capture.

@@ -86,3 +86,23 @@ def test_device_mesh_and_shard_linear(pkg):
     assert torch.equal(row.weight, lin.weight[:, :3]) and torch.equal(row.bias, lin.bias)
     with pytest.raises(TypeError):
         shard_linear(torch.nn.ReLU(), 0, m)
+
+
+@pytest.mark.parametrize("world,n", [(2, 511), (3, 625), (4, 1022), (8, 1001)])
+def test_peer_gather_branch_is_the_same_on_every_rank(pkg, world, n):
+    """With ragged shards a rank's own byte count straddles any size threshold (N = 511 on 2 ranks: 256 and 255 rows,
+    exactly 32 MiB and just below).  The choice between the peer-store gather and the library collective must not
+    depend on it, or one rank waits at the flag barrier while the other sits in a collective."""
+    from distributed_xfold_b200 import row_sharded
+    ld = (n + 7) // 8 * 8
+    row_bytes = 128 * ld * 2                                    # one row of the b operand [rows, 128, ld]
+    shards = [row_sharded.RowSharding(n, world=world, rank=r) for r in range(world)]
+    assert len({sh.r for sh in shards}) > 1                     # the partition is ragged
+    for threshold in (shards[0].r * row_bytes, shards[-1].r * row_bytes + 16, n * row_bytes, n * row_bytes + 16, 1):
+        picks = []
+        for sh in shards:
+            sh.peer = object()                                  # peer exchange available on every rank
+            sh.PEER_GATHER_MIN_BYTES = threshold
+            picks.append(sh.uses_peer_gather(row_bytes, operand_b=True))
+            assert not sh.uses_peer_gather(row_bytes, operand_b=False)   # bias / logit gathers never take the peer buffer
+        assert len(set(picks)) == 1, (threshold, picks)

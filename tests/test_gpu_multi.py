@@ -67,7 +67,7 @@ def _rank_main(rank, world, port, n, pad, use_peer, channel, ret):
         assert sh.enable_peer_exchange(f"cuda:{rank}"), getattr(sh, "peer_error", "")
         # at these sizes only the b operand (2 MB per rank) is above 1 MB: it takes the peer-store gather, as it does
         # at benchmark size with the default threshold
-        sh.peer.GATHER_MIN_BYTES = 1 << 20
+        sh.PEER_GATHER_MIN_BYTES = 1 << 20
     zd = z[sh.rows].to(BF).cuda().contiguous()
     sd = s.to(BF).cuda().contiguous()
     pmd = pm.cuda()

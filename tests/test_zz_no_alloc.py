@@ -59,3 +59,26 @@ def test_static_scratch_rejects_oversize(ops, oracle):
     assert rc == _cabi.XFOLD_ERR_ARG
     msg = lib.xfold_last_error(_cabi.ctx(0)).decode()
     assert "static scratch" in msg and "workspace" in msg
+
+
+@pytest.mark.parametrize("c,f,last_ok", [(128, 512, 13105), (384, 1536, 4368)])
+def test_static_scratch_edge_of_limit(ops, oracle, c, f, last_ok):
+    """The documented capacity is exact: `last_ok` rows run (and match the workspace version), one row more is refused."""
+    from distributed_xfold_b200 import _cabi
+    lib = _cabi.load()
+    limit = lib.xfold_transition_static_max_bytes()
+    assert lib.xfold_transition_workspace_bytes(last_ok, c, f) <= limit < lib.xfold_transition_workspace_bytes(last_ok + 1, c, f)
+    g = torch.Generator().manual_seed(5 + c)
+    w = ops.PackedTransition(oracle.make_transition_state(g, "", c), "", "cuda")
+    x = torch.randn(last_ok + 1, c, generator=g).to(BF)
+    ref = x[:last_ok].cuda().contiguous()
+    ops.transition_(ref, w)
+    got = x.cuda().contiguous()
+    st = torch.cuda.current_stream(0).cuda_stream
+    assert lib.xfold_transition_static_fwd(_cabi.ctx(0), got.data_ptr(), last_ok, c, f, C.byref(w.c), st) == 0
+    ops.synchronize_and_check()
+    assert torch.equal(got[:last_ok], ref) and torch.equal(got[last_ok], x[last_ok].cuda())   # the extra row is untouched
+    assert lib.xfold_transition_static_fwd(_cabi.ctx(0), got.data_ptr(), last_ok + 1, c, f, C.byref(w.c), st) == _cabi.XFOLD_ERR_ARG
+    # a row count whose byte size would wrap around is refused as well, before any launch
+    assert lib.xfold_transition_static_fwd(_cabi.ctx(0), got.data_ptr(), 1 << 62, c, f, C.byref(w.c), st) == _cabi.XFOLD_ERR_ARG
+    ops.synchronize_and_check()
