@@ -360,6 +360,30 @@ def pairformer_block_sharded(state: State, prefix: str, pair, pair_mask, single,
     return pair, single
 
 
+def pairformer_block_rounded(state: State, prefix: str, pair, pair_mask, single, seq_mask, dtype=torch.bfloat16,
+                             n_heads: int = 16, n_heads_pair: int = 4):
+    """``pairformer_block`` with the representations STORED in ``dtype`` between sub-layers and fp32 arithmetic
+    inside them: every sub-layer reads the rounded representation, its update is rounded, and the sum is rounded
+    again.  These are the roundings any implementation has that keeps z and s in ``dtype`` (the reference's bf16
+    wrappers cast on entry and exit of every fused op, nn/d_triangle_multiplication.py:187-190,
+    nn/d_attention.py:75-78), so the distance of this function from ``pairformer_block`` is the error floor of
+    ``dtype`` storage for a given depth and set of weights, whatever the kernels inside do."""
+    def r(t):
+        return t.to(dtype).float()
+    pair, single = r(pair), r(single)
+    pair = r(pair + r(triangle_multiplication(state, prefix + "triangle_multiplication_outgoing.", pair, pair_mask, True)))
+    pair = r(pair + r(triangle_multiplication(state, prefix + "triangle_multiplication_incoming.", pair, pair_mask, False)))
+    pair = r(pair + r(grid_self_attention(state, prefix + "pair_attention1.", pair, pair_mask, pair, False, n_heads_pair)))
+    pair = r(pair + r(grid_self_attention(state, prefix + "pair_attention2.", pair, pair_mask, pair, True, n_heads_pair)))
+    pair = r(pair + r(transition(state, prefix + "pair_transition.", pair)))
+    pl = linear(layer_norm(pair, _get(state, prefix, "single_pair_logits_norm.weight"),
+                           _get(state, prefix, "single_pair_logits_norm.bias")),
+                state[prefix + "single_pair_logits_projection.weight"]).permute(2, 0, 1)
+    single = r(single + r(self_attention(state, prefix + "single_attention_.", single, seq_mask, pl, None, n_heads)))
+    single = r(single + r(transition(state, prefix + "single_transition.", single)))
+    return pair, single
+
+
 def pairformer_stack(state: State, pair, pair_mask, single, seq_mask, num_blocks: int, row_chunk: int = 0):
     """d_alphafold3.py:242-244: the 48-block loop of DistributeEvoformer.forward."""
     for i in range(num_blocks):
