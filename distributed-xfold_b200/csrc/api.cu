@@ -59,15 +59,18 @@ static bool load_encode() {
 }
 
 bool make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
-                       uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2) {
+                       uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2, int swizzle_bytes) {
   if (!g_encode) return false;
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {s1 * 2, s2 * 2};
   cuuint32_t box[3] = {b0, b1, b2};
   cuuint32_t es[3] = {1, 1, 1};
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (strides[0] & 15) || (strides[1] & 15)) return false;
+  if ((swizzle_bytes != 64 && swizzle_bytes != 128) || b0 * 2 > (uint32_t)swizzle_bytes) return false;
   CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, es,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }

@@ -1,0 +1,618 @@
+// Gated attention for head dim 32 (TriangleAttention, 4 heads; AttentionPairBias with its 24-wide heads padded to
+// 32, 16 heads): the softmax warps never touch global memory, and sixteen of them are resident per SM.
+//
+// Work item = 128 queries of one batch row x 4 heads; CTAs are persistent (one per SM) and run their items' 64-key
+// blocks as one continuous sequence.
+//   warp 0        : TMA producer.  Q per item (128 rows x 4 heads x 32 = two 64-column boxes); per 64-key block the K
+//                   tile (+ the 2 KB mask-bias tile) and the V tile, two stages each.
+//   warps 1..4    : tcgen05.mma issuers, one per head, so that no head ever waits for another.  Per block:
+//                       S  = Q K^T              (K = 32, N = 64)
+//                       S += E1 * Mext^T        (K = 16; column 0 of E1 is all ones, column 0 of Mext is the
+//                                                additive mask bias of each key)
+//                       O += P V                (K = 64, N = 32; P read from tensor memory, O stays there for the item)
+//                   Each issuer also fetches its head's pair-bias tiles (32-key halves, a ring of three).
+//   warps 5..20   : four softmax warpgroups, one per head, one thread per query row.
+//
+// Why this shape.  The exponential unit (16 results per clock and SM) bounds the kernel: 4 x 128 x 64 exponentials
+// per block are 2048 clocks of it.  A softmax warp spends much of a block waiting (tensor-memory loads and stores,
+// barrier round trips, the dependent chain into the exponential); with two such warps per scheduler the unit idled
+// half of the time.  Four warps per scheduler need a thread to fit in ~96 registers, so a thread holds HALF a block
+// (32 logits) at a time: load 32 logits, sweep, store 16 packed probabilities, load the other 32 (after which the
+// logits buffer is free and the issuer already computes the next block's), sweep, store, publish.  Tensor memory is
+// then exactly full with single buffers: 4 x 64 columns of logits, 4 x 32 of output, 4 x 32 of probabilities.
+//
+// The sweep exponentiates against the running reference exponent m_ref of the PREVIOUS halves,
+//     x = s * log2(e) - m_ref (fp32) -> fp16x2,  + bias' (fp16x2; bias' = bias * log2(e) as delivered),
+//     running max (fp16x2), ex2.approx.f16x2, row sum (fp16x2 partial sums), P as fp16,
+// and only looks at the maximum afterwards: if some row of the warp saw x > 8 (P > 256; fp16 would overflow beyond
+// 2^16), the warp takes the exact path -- fp32 row maximum of the half still held in registers, O (tensor memory),
+// the row sum and, in a block's second half, the stored first half of P rescaled, the sweep repeated.  The first half
+// of an item always takes the exact path.  With trained or random weights the repeat is rare afterwards.
+//
+// The pair bias arrives as FP16 [head][query][key], multiplied by log2(e) (key contiguous, row pitch a multiple of
+// 8); TMA lays a [128 queries][32 keys] tile out with the 64-byte swizzle, so the per-row 16-byte reads of the
+// softmax threads are bank-conflict free.
+#include <cuda_fp16.h>
+
+#include "internal.h"
+#include "umma.cuh"
+
+namespace xf {
+
+struct Attn3Args {
+  int S, B;
+  int q_col0, k_col0, v_col0, g_col0;
+  int transposed;
+  const bf16* qkvg;
+  long long seq_stride, batch_stride;
+  const bf16* mext;  // [B or 1][KB][2048] bf16: un-swizzled K-major [128 keys][16] tiles, column 0 = mask bias
+  long long mext_batch_stride;  // elements; 0 when one mask row serves every batch row
+  bf16* out;
+  long long out_seq_stride, out_batch_stride;
+  int heads;
+  int* status;
+};
+
+constexpr int A3_CTRL = 5;                      // TMA producer + four MMA issuers
+constexpr int A3_THREADS = (A3_CTRL + 16) * 32;  // + sixteen softmax warps
+constexpr uint32_t A3_Q = 32768;                 // [2 boxes][128 rows][64 columns]
+constexpr uint32_t A3_KV = 16384;                // [2 boxes][64 rows][64 columns]
+constexpr uint32_t A3_BT = 8192;                 // bias tile [128 queries][32 keys] fp16
+constexpr int A3_BS = 3;                         // bias tiles in flight per head
+constexpr uint32_t A3_OFF_Q = 0, A3_OFF_K = A3_Q, A3_OFF_V = A3_OFF_K + 2 * A3_KV, A3_OFF_BIAS = A3_OFF_V + 2 * A3_KV,
+                   A3_OFF_E1 = A3_OFF_BIAS + 4 * A3_BS * A3_BT, A3_OFF_MEXT = A3_OFF_E1 + 4096,
+                   A3_OFF_BAR = A3_OFF_MEXT + 2 * 2048;
+constexpr uint32_t A3_SMEM = A3_OFF_BAR + 512 + 1024;
+// TMEM columns: logits S of head w at w*64 (64 columns); output O of head w at 256 + w*32; probabilities P of head w at
+// 384 + w*32 (64 keys as 32 fp16 pairs).
+constexpr uint32_t A3_TM_O = 256, A3_TM_P = 384;
+
+__device__ __forceinline__ float ex2f_(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void tmem_ld16_(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16_(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32_(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(A3_THREADS, 1)
+attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmkv,
+             const __grid_constant__ CUtensorMap tmb, const Attn3Args p) {
+  constexpr int D = 32;
+  constexpr float LOG2E = 1.4426950408889634f;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sQ = smem + A3_OFF_Q;
+  uint8_t* sK = smem + A3_OFF_K;        // [block & 1]
+  uint8_t* sV = smem + A3_OFF_V;        // [block & 1]
+  uint8_t* sBias = smem + A3_OFF_BIAS;  // [head][half % 3]
+  uint8_t* sE1 = smem + A3_OFF_E1;
+  uint8_t* sMext = smem + A3_OFF_MEXT;  // [block & 1], 2 KB each
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + A3_OFF_BAR);
+  uint64_t* q_full = bars;         // [1]
+  uint64_t* q_empty = bars + 1;    // [1] all four issuers have committed the item's last logits
+  uint64_t* k_full = bars + 2;     // [2]
+  uint64_t* k_empty = bars + 4;    // [2] all four issuers have committed the block's logits
+  uint64_t* v_full = bars + 6;     // [2]
+  uint64_t* v_empty = bars + 8;    // [2] all four issuers have committed the block's P V product
+  uint64_t* s_full = bars + 10;    // [head] logits of a block are in TMEM
+  uint64_t* s_free = bars + 14;    // [head] the softmax warps hold the block's logits in registers (and have used up the
+                                   //        bias tile of its first half)
+  uint64_t* p_ready = bars + 18;   // [head] P of a block is in TMEM (and the bias tile of its second half is used up)
+  uint64_t* pv_done = bars + 22;   // [head] P V product of a block complete
+  uint64_t* b_full = bars + 26;    // [head][3] bias tile landed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 38);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const AbortCtx ab{cta_abort, p.status};
+  const int KB = (p.S + 63) / 64;
+  // Persistent CTA: work items (batch row, head group of 4, query tile), batch row slowest so that the K / V rows of
+  // the ~gridDim.x items in flight stay in L2.  Every role walks the same sequence of blocks; block numbers (and with
+  // them buffer indices and barrier phases) keep counting across items.
+  const int QT = (p.S + 127) / 128, HG = p.heads / 4;
+  const long long n_items = (long long)p.B * HG * QT;
+  const uint32_t my_items = n_items > blockIdx.x ? uint32_t((n_items - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
+  const uint32_t G = my_items * uint32_t(KB);  // blocks this CTA processes in total (the launcher bounds items * KB to 2^30)
+  auto decode = [&](uint32_t it, int& qt, int& hg, int& b) {
+    const uint32_t t = blockIdx.x + it * gridDim.x;
+    qt = int(t % uint32_t(QT));
+    hg = int((t / uint32_t(QT)) % uint32_t(HG));
+    b = int(t / uint32_t(QT * HG));
+  };
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, 4);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 4);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 4);
+    }
+    for (int w = 0; w < 4; ++w) {
+      mbar_init(&s_full[w], 1);
+      mbar_init(&s_free[w], 4);   // one elected lane per softmax warp
+      mbar_init(&p_ready[w], 4);
+      mbar_init(&pv_done[w], 1);
+      for (int s = 0; s < A3_BS; ++s) mbar_init(&b_full[w * A3_BS + s], 1);
+    }
+    *cta_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmq);
+    tma_prefetch_desc(&tmkv);
+    tma_prefetch_desc(&tmb);
+  }
+  // constant operand E1: un-swizzled [128][16] tile whose column 0 is all ones
+  for (uint32_t i = threadIdx.x; i < 4096 / 16; i += A3_THREADS) reinterpret_cast<uint4*>(sE1)[i] = make_uint4(0, 0, 0, 0);
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    const uint32_t m = threadIdx.x;
+    *reinterpret_cast<uint16_t*>(sE1 + (m >> 3) * 256 + (m & 7) * 16) = 0x3F80;  // bf16 1.0
+  }
+  fence_proxy_async_smem();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      uint32_t j = 0;  // block number
+      bool okay = true;
+      for (uint32_t it = 0; it < my_items && okay; ++it) {
+        int qt, hg, b;
+        decode(it, qt, hg, b);
+        if (!mbar_wait(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(q_full, A3_Q);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int col = p.q_col0 + hg * 128 + x * 64;
+          if (p.transposed) tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, b, qt * 128);
+          else tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, qt * 128, b);
+        }
+        const bf16* mrow = p.mext + (long long)b * p.mext_batch_stride;
+        for (int kb = 0; kb < KB; ++kb, ++j) {
+          const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
+          if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          mbar_arrive_expect_tx(&k_full[st], A3_KV + 2048);
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int col = p.k_col0 + hg * 128 + x * 64;
+            if (p.transposed) tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, b, kb * 64);
+            else tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, kb * 64, b);
+          }
+          bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
+          if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          mbar_arrive_expect_tx(&v_full[st], A3_KV);
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            const int col = p.v_col0 + hg * 128 + x * 64;
+            if (p.transposed) tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, b, kb * 64);
+            else tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, kb * 64, b);
+          }
+        }
+      }
+    }
+  } else if (warp < A3_CTRL) {
+    // ------------------------------------------------------------------------------------------- MMA issuer of head w
+    if (lane == 0) {
+      const int w = warp - 1;
+      constexpr uint32_t idesc_s = make_idesc(128, 64);
+      constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
+                                                                  // projection buffer are written as fp16 by the GEMM
+      const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
+      // head w lives in 64-column box w / 2, in the upper or lower 64 bytes of its 128-byte swizzled rows
+      const uint32_t q_addr = smem_u32(sQ) + uint32_t(w >> 1) * (A3_Q / 2) + uint32_t(w & 1) * 64u;
+      const uint32_t k_off = uint32_t(w >> 1) * (A3_KV / 2) + uint32_t(w & 1) * 64u;
+      uint64_t* my_bfull = b_full + w * A3_BS;
+      uint8_t* my_bias = sBias + w * A3_BS * A3_BT;
+      bool okay = true;
+      // next block whose logits are issued (one ahead of the softmax), tracked without divisions
+      uint32_t aj = 0, ait = 0;
+      int akb = 0, aqt, ahg, ab_;
+      decode(0, aqt, ahg, ab_);
+      auto issue_s = [&]() -> bool {
+        const uint32_t ks = aj & 1u, kpar = (aj >> 1) & 1u;
+        if (akb == 0 && !mbar_wait(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+        if (!mbar_wait(&k_full[ks], kpar, ab, XF_ERR_WAIT_FULL)) return false;
+        tc_fence_after();
+        const uint32_t d = tmem_base + w * 64;
+        const uint64_t qd = make_sdesc(q_addr, 16, 1024);
+        const uint64_t kd = make_sdesc(smem_u32(sK) + ks * A3_KV + k_off, 16, 1024);
+        const uint64_t mxd = make_sdesc_noswizzle(smem_u32(sMext) + ks * 2048, 128, 256);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) umma_ss(d, qd + 2 * k, kd + 2 * k, idesc_s, k ? 1u : 0u);
+        umma_ss(d, e1d, mxd, idesc_s, 1u);
+        umma_commit(&s_full[w]);
+        umma_commit(&k_empty[ks]);
+        if (akb == KB - 1) umma_commit(q_empty);  // last use of this item's Q tile
+        ++aj;
+        if (++akb == KB) {
+          akb = 0;
+          ++ait;
+          decode(ait, aqt, ahg, ab_);
+        }
+        return true;
+      };
+      // next bias tile to fetch: half bi of the CTA's block sequence = (item, key block, half)
+      uint32_t bi = 0, bslot = 0, bit = 0;
+      int bkb = 0, bh = 0, bqt, bhg, bb_;
+      decode(0, bqt, bhg, bb_);
+      auto issue_bias = [&]() {
+        mbar_arrive_expect_tx(&my_bfull[bslot], A3_BT);
+        tma_load_3d(my_bias + bslot * A3_BT, &tmb, &my_bfull[bslot], bkb * 64 + bh * 32, bqt * 128, bhg * 4 + w);
+        ++bi;
+        if (++bslot == A3_BS) bslot = 0;
+        if (++bh == 2) {
+          bh = 0;
+          if (++bkb == KB) {
+            bkb = 0;
+            ++bit;
+            decode(bit, bqt, bhg, bb_);
+          }
+        }
+      };
+      const uint32_t n_half = 2u * G;
+      while (bi < uint32_t(A3_BS) && bi < n_half) issue_bias();
+      if (G > 0) okay = issue_s();
+      int kb = 0;  // key block of block g within its item
+      for (uint32_t g = 0; g < G && okay; ++g) {
+        const uint32_t par = g & 1u, vs = g & 1u, vpar = (g >> 1) & 1u;
+        // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1, and the bias tile of the
+        // first half of block g has been used up
+        if (!mbar_wait(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (g + 1 < G && !issue_s()) break;
+        if (bi < n_half) issue_bias();
+        const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
+        if (!mbar_wait(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
+        tc_fence_after();
+        const uint32_t pt = tmem_base + A3_TM_P + w * 32;
+        const uint32_t vbase = smem_u32(sV) + vs * A3_KV + k_off;
+        const uint32_t d = tmem_base + A3_TM_O + w * 32;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t bd = make_sdesc(vbase + ks * 2048, 16384, 1024);  // V is N-major: 16 keys = 2048 B
+          umma_ts(d, pt + ks * 8, bd, idesc_pv, (kb | ks) ? 1u : 0u);      // 16 keys = 8 columns of P; O accumulates
+        }
+        umma_commit(&pv_done[w]);
+        umma_commit(&v_empty[vs]);
+        if (bi < n_half) issue_bias();
+        if (++kb == KB) kb = 0;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------------------------------- softmax warps
+    const int w = (warp - A3_CTRL) >> 2;
+    const int q4 = warp & 3;  // TMEM lane quarter this warp may access
+    const int row = q4 * 32 + lane;
+    const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
+    const uint32_t s_addr = tmem_base + w * 64 + lane_addr;
+    const uint32_t o_addr = tmem_base + A3_TM_O + w * 32 + lane_addr;
+    const uint32_t p_addr = tmem_base + A3_TM_P + w * 32 + lane_addr;
+    const uint32_t bsw = uint32_t(row >> 1) & 3u;  // 64-byte swizzle: 16-byte chunk index XOR (row / 2) % 4
+    const uint8_t* my_bias = sBias + w * A3_BS * A3_BT + row * 64;
+    uint64_t* my_bfull = b_full + w * A3_BS;
+    const uint32_t FULL = 0xffffffffu;
+    uint32_t g = 0, bslot = 0, bpar = 0;  // block number; bias ring position and phase
+    bool okay = true;
+    for (uint32_t it = 0; it < my_items && okay; ++it) {
+      int qt, hg, b;
+      decode(it, qt, hg, b);
+      const int qi = qt * 128 + row;
+      const bool qvalid = qi < p.S;
+      // m_ref: exponent offset in use (log2 units); it follows the running maximum lazily (see the file header).
+      float m_ref = -3.0e38f, l_run = 0.f;
+      for (int kb = 0; kb < KB && okay; ++kb, ++g) {
+        const uint32_t par = g & 1u;
+        okay = __all_sync(FULL, mbar_wait(&s_full[w], par, ab, XF_ERR_WAIT_ATTN));
+        if (!okay) break;
+        tc_fence_after();
+#pragma unroll 1
+        for (int h = 0; h < 2 && okay; ++h) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + h * 32, r);
+          const uint8_t* bt = my_bias + bslot * A3_BT;
+          okay = __all_sync(FULL, mbar_wait(&my_bfull[bslot], bpar, ab, XF_ERR_WAIT_ATTN));
+          tmem_ld_wait();
+          if (!okay) break;
+          if (h == 1) {  // both halves of S(g) have been read: the issuer may overwrite the buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free[w]);
+          }
+          bool exact = (kb == 0 && h == 0);
+          __half2 hs[4];
+          uint32_t pk[16];
+          for (;;) {
+            if (exact) {
+              // fp32 maximum of this half; move the reference if it grew by more than 2^8
+              float mx0 = -3.0e38f, mx1 = -3.0e38f;
+#pragma unroll
+              for (int c4 = 0; c4 < 4; ++c4) {
+                const uint4 bq = *reinterpret_cast<const uint4*>(bt + ((uint32_t(c4) ^ bsw) << 4));
+                const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 bf = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
+                  mx0 = fmaxf(mx0, fmaf(__uint_as_float(r[c4 * 8 + 2 * e]), LOG2E, bf.x));
+                  mx1 = fmaxf(mx1, fmaf(__uint_as_float(r[c4 * 8 + 2 * e + 1]), LOG2E, bf.y));
+                }
+              }
+              const float mx = fmaxf(mx0, mx1);
+              const bool grow = mx > m_ref + 8.f;
+              if (__any_sync(FULL, grow)) {
+                const float m_new = grow ? mx : m_ref;
+                const float alpha = ex2f_(m_ref - m_new);
+                m_ref = m_new;
+                l_run *= alpha;
+                if (kb > 0) {
+                  // every earlier P V product of the item must have landed before O is rescaled
+                  okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
+                  if (!okay) break;
+                  tc_fence_after();
+                  uint32_t o[32];
+                  tmem_ld32(o_addr, o);
+                  tmem_ld_wait();
+#pragma unroll
+                  for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                  tmem_st32_(o_addr, o);
+                  tmem_st_wait_();
+                }
+                if (h == 1) {  // the first half of this block's P is already stored: bring it to the new reference
+                  uint32_t q[16];
+                  tmem_ld16_(p_addr, q);
+                  tmem_ld_wait();
+                  const __half2 a2 = __float2half2_rn(alpha);
+#pragma unroll
+                  for (int e = 0; e < 16; ++e) {
+                    const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&q[e]), a2);
+                    q[e] = *reinterpret_cast<const uint32_t*>(&v);
+                  }
+                  tmem_st16_(p_addr, q);
+                  tmem_st_wait_();
+                }
+              }
+            }
+            // the sweep: exponent, fp16x2 pack, bias, running max, exponential, row sum (8 keys per 16-byte bias read)
+            const float nm = -m_ref;
+            __half2 hm = __float2half2_rn(-65504.f);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) hs[e] = __float2half2_rn(0.f);
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              const uint4 bq = *reinterpret_cast<const uint4*>(bt + ((uint32_t(c4) ^ bsw) << 4));
+              const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float x0 = fmaf(__uint_as_float(r[c4 * 8 + 2 * e]), LOG2E, nm);
+                const float x1 = fmaf(__uint_as_float(r[c4 * 8 + 2 * e + 1]), LOG2E, nm);
+                const __half2 xh = __hadd2(__floats2half2_rn(x0, x1), *reinterpret_cast<const __half2*>(&bw[e]));
+                hm = __hmax2(hm, xh);
+                uint32_t ph;
+                asm("ex2.approx.f16x2 %0, %1;" : "=r"(ph) : "r"(*reinterpret_cast<const uint32_t*>(&xh)));
+                hs[e] = __hadd2(hs[e], *reinterpret_cast<const __half2*>(&ph));
+                pk[c4 * 4 + e] = ph;
+              }
+            }
+            if (exact) break;
+            const float2 bm = __half22float2(hm);
+            if (!__any_sync(FULL, fmaxf(bm.x, bm.y) > 8.f)) break;
+            exact = true;  // some row outgrew the reference: exact maximum, rescale, sweep again
+          }
+          if (!okay) break;
+          float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(hs[e]);
+            ls0 += f.x;
+            ls1 += f.y;
+          }
+          l_run += ls0 + ls1;
+          if (h == 0 && g > 0) {
+            // the P V product of the previous block must have read P before it is overwritten
+            okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
+            if (!okay) break;
+            tc_fence_after();
+          }
+          tmem_st16_(p_addr + h * 16, pk);
+          if (++bslot == A3_BS) { bslot = 0; bpar ^= 1u; }
+          tmem_st_wait_();
+        }
+        if (!okay) break;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_ready[w]);
+      }
+      if (!okay || KB == 0) break;
+      // item epilogue: O / l, gate, store
+      okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
+      if (!okay) break;
+      tc_fence_after();
+      uint32_t o[32];
+      tmem_ld32(o_addr, o);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (qvalid) {
+        const int col = hg * 128 + w * D;
+        const float inv = __fdividef(1.f, l_run);
+        const bf16* grow_ = p.qkvg + (long long)b * p.batch_stride + (long long)qi * p.seq_stride + p.g_col0 + col;
+        bf16* orow = p.out + (long long)b * p.out_batch_stride + (long long)qi * p.out_seq_stride + col;
+#pragma unroll
+        for (int g8 = 0; g8 < D / 8; ++g8) {
+          const uint4 gu = *reinterpret_cast<const uint4*>(grow_ + g8 * 8);
+          const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
+          uint32_t ow[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float o0 = __uint_as_float(o[g8 * 8 + 2 * e]) * inv * sigmoidf_fast(bf16_lo(gw[e]));
+            const float o1 = __uint_as_float(o[g8 * 8 + 2 * e + 1]) * inv * sigmoidf_fast(bf16_hi(gw[e]));
+            ow[e] = pack_bf16x2(o0, o1);
+          }
+          *reinterpret_cast<uint4*>(orow + g8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*cta_abort && threadIdx.x == 0) {
+    // an aborted wait may have left copies in flight: give them time to land before the CTA's memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {}
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Mask-bias tiles: out[b][kb] is an un-swizzled K-major [128 keys][16] bf16 tile (core matrices of
+// 8 keys x 8 columns, 128 B each; the two column halves 128 B apart, 8-key groups 256 B apart) whose
+// column 0 holds 1e9 * (mask[b][k] - 1) for k < S and -1e30 for the padding of the last tile.
+__global__ void mext_kernel(const float* __restrict__ mask, long long mask_ld, bf16* __restrict__ out, int B, int S,
+                            int KB) {
+  const long long n = (long long)B * KB * 128;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int r = int(idx & 127);
+    const long long tile = idx >> 7;
+    const int kb = int(tile % KB);
+    const long long bb = tile / KB;
+    const int k = kb * 128 + r;
+    float v = -1.0e30f;
+    // 1e9 * (mask - 1) as in the reference, floored at -60000: any such logit still exponentiates to exactly 0
+    // next to an unmasked one, while a row whose keys are ALL masked keeps fp32-resolvable logits (at 1e9 the
+    // fp32 spacing is 64, which would turn into exponents of +-128 and overflow the fp16 exponentials)
+    if (k < S) v = mask ? fmaxf(1.0e9f * (mask[bb * mask_ld + k] - 1.f), -60000.f) : 0.f;
+    uint4 lo = make_uint4(uint32_t(__bfloat16_as_ushort(__float2bfloat16(v))), 0, 0, 0);
+    uint8_t* t = reinterpret_cast<uint8_t*>(out) + tile * 4096 + (r >> 3) * 256 + (r & 7) * 16;
+    *reinterpret_cast<uint4*>(t) = lo;
+    *reinterpret_cast<uint4*>(t + 128) = make_uint4(0, 0, 0, 0);
+  }
+}
+
+int launch_mext(Ctx* c, const float* mask, long long mask_ld, bf16* out, int B, int S, cudaStream_t st) {
+  const int KB = (S + 127) / 128;
+  const long long n = (long long)B * KB * 128;
+  if (n <= 0) return XFOLD_OK;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 8192) blocks = 8192;
+  ProfScope ps(c, XFOLD_K_MASK_BIAS, st);
+  mext_kernel<<<(int)blocks, 256, 0, st>>>(mask, mask_ld, out, B, S, KB);
+  return check_launch(c, "mext_kernel");
+}
+
+// fp32 [H][S][S] -> 16-bit [H][S][ldq] (same query-major order, padded row pitch): FP16 values times log2(e), the operand
+// the kernel's pair-bias tensor map expects (the kernel works in base 2 and adds the tile as it is).
+__global__ void bias_convert_kernel(const float* __restrict__ in, __half* __restrict__ out, long long rows, int S, int ldq) {
+  const long long n = rows * ldq;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long r = idx / ldq;
+    const int k = int(idx % ldq);
+    out[idx] = __float2half_rn(k < S ? fminf(fmaxf(in[r * S + k] * 1.4426950408889634f, -60000.f), 60000.f) : 0.f);
+  }
+}
+
+int launch_bias_transpose(Ctx* c, const float* in, bf16* out, int H, int S, int ldq, cudaStream_t st) {
+  if (H <= 0 || S <= 0) return XFOLD_OK;
+  const long long rows = (long long)H * S;
+  long long blocks = (rows * ldq + 255) / 256;
+  if (blocks > 16384) blocks = 16384;
+  ProfScope ps(c, XFOLD_K_MASK_BIAS, st);
+  bias_convert_kernel<<<(int)blocks, 256, 0, st>>>(in, reinterpret_cast<__half*>(out), rows, S, ldq);
+  return check_launch(c, "bias_convert_kernel");
+}
+
+// qkvg: projection buffer ([B][S][width], or [S][B][width] when transposed); biasT: 16-bit [heads][query][ldq] holding FP16
+// values; mext: tiles from launch_mext ([B][KB][2048] or one row shared by all batch rows when mext_rows == 1).
+int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0, int k_col0,
+                      int v_col0, int g_col0, int heads, const bf16* biasT, int ldq, const bf16* mext, int mext_rows,
+                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st) {
+  if ((width & 7) || (ldq & 7) || (heads & 3) || ((q_col0 | k_col0 | v_col0 | g_col0) & 7))
+    return fail(c, XFOLD_ERR_ARG, "attention: width, column offsets and bias pitch must be multiples of 8, heads a multiple of 4");
+  if (S <= 0 || B <= 0) return XFOLD_OK;
+  CUtensorMap tmq, tmkv, tmb;
+  bool ok;
+  Attn3Args a;
+  if (!transposed) {
+    ok = make_tmap_bf16_3d(&tmq, qkvg, width, S, B, width, (uint64_t)width * S, 64, 128, 1) &&
+         make_tmap_bf16_3d(&tmkv, qkvg, width, S, B, width, (uint64_t)width * S, 64, 64, 1);
+    a.seq_stride = width;
+    a.batch_stride = (long long)S * width;
+  } else {
+    ok = make_tmap_bf16_3d(&tmq, qkvg, width, B, S, width, (uint64_t)width * B, 64, 1, 128) &&
+         make_tmap_bf16_3d(&tmkv, qkvg, width, B, S, width, (uint64_t)width * B, 64, 1, 64);
+    a.seq_stride = (long long)B * width;
+    a.batch_stride = width;
+  }
+  // dims: key, query, head; [128 queries][32 keys] tiles with 64-byte rows
+  ok = ok && make_tmap_bf16_3d(&tmb, biasT, S, S, heads, ldq, (uint64_t)ldq * S, 32, 128, 1, 64);
+  if (!ok) return fail(c, XFOLD_ERR_ARG, "attention: cannot encode tensor maps");
+  const int KB = (S + 127) / 128;  // 128-key mask tiles (two 64-key blocks each)
+  a.S = S;
+  a.B = B;
+  a.q_col0 = q_col0;
+  a.k_col0 = k_col0;
+  a.v_col0 = v_col0;
+  a.g_col0 = g_col0;
+  a.transposed = transposed;
+  a.qkvg = qkvg;
+  a.mext = mext;
+  a.mext_batch_stride = mext_rows == 1 ? 0 : (long long)KB * 2048;
+  a.out = out;
+  a.out_seq_stride = out_seq_stride;
+  a.out_batch_stride = out_batch_stride;
+  a.status = c->d_status;
+  a.heads = heads;
+  static bool attr_done[8] = {false};
+  if (!attr_done[c->device & 7]) {
+    cudaError_t e = cudaFuncSetAttribute(attn3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A3_SMEM);
+    if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "attention smem attribute: %s", cudaGetErrorString(e));
+    attr_done[c->device & 7] = true;
+  }
+  const long long items = (long long)((S + 127) / 128) * (heads / 4) * B;
+  if (items * ((S + 63) / 64) >= (1ll << 30)) return fail(c, XFOLD_ERR_ARG, "attention: batch x heads x sequence too large for one launch");
+  const int grid = (int)(items < c->sm_count ? items : c->sm_count);
+  ProfScope ps(c, c->attn_tag, st);
+  attn3_kernel<<<grid, A3_THREADS, A3_SMEM, st>>>(tmq, tmkv, tmb, a);
+  return check_launch(c, "attn3_kernel");
+}
+
+}  // namespace xf

@@ -61,9 +61,9 @@ int check_launch(Ctx* c, const char* what);
 
 // ---- tensor maps --------------------------------------------------------------------------
 // bf16 tensor of rank 3, innermost stride 1; s1/s2 are strides of dims 1/2 in ELEMENTS.
-// 128-byte swizzle, zero fill outside the extents.
+// 128-byte swizzle (or 64-byte, for boxes whose rows are 64 bytes), zero fill outside the extents.
 bool make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
-                       uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2);
+                       uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2, int swizzle_bytes = 128);
 
 // ---- GEMM ---------------------------------------------------------------------------------
 enum GemmEpi : int { EPI_PLAIN = 0, EPI_GATE_RESID = 1, EPI_SWIGLU = 2, EPI_TRIMUL_AB = 3 };

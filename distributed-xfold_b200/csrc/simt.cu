@@ -2,6 +2,8 @@
 // produces the attention pair bias), LayerNorm of a channel-major tensor with a transposing
 // write-back, and the element-wise pieces of the diffusion transformer (AdaLN modulation, gates).
 // One warp per row, 8-byte vector accesses, fp32 statistics, warp-shuffle reductions.
+#include <cuda_fp16.h>
+
 #include "internal.h"
 #include "umma.cuh"
 
@@ -16,11 +18,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ---------------------------------------------------------------------------------------------
 // y = LN(x) * gamma + beta  (gamma/beta may be null), rows of C bf16; optional
 // proj[h][row] = sum_c y[c] * pw[h][c]  (fp32, computed from the un-rounded y)
-// proj_bf16 (instead of proj) is the attention kernels' pair-bias operand: bf16, and multiplied by log2(e), because
-// the head-dim-32 attention kernel exponentiates in base 2 and adds the bias tile as it is.
+// proj_bf16 (instead of proj) is the attention kernel's pair-bias operand: 16-bit, holding FP16 values (the buffer
+// is only typed bf16) multiplied by log2(e), because the head-dim-32 attention kernel exponentiates in base 2 and adds
+// the bias tile, as it is, to fp16x2 exponent arguments.
 // optional modulation: y = sigmoid(scale[row % mod_rows][c]) * y + shift[row % mod_rows][c]  (AdaLN)
 // ---------------------------------------------------------------------------------------------
 constexpr float kBiasLog2e = 1.4426950408889634f;
+// fp16 bit pattern of v * log2(e) in a 16-bit slot of the bias buffer (clamped to the finite fp16 range)
+__device__ __forceinline__ bf16 bias16(float v) {
+  const __half h = __float2half_rn(fminf(fmaxf(v * kBiasLog2e, -60000.f), 60000.f));
+  return *reinterpret_cast<const bf16*>(&h);
+}
 
 template <int C, int H>
 __global__ void __launch_bounds__(256)
@@ -139,7 +147,7 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
           const float tot = acc[0] + __shfl_xor_sync(0xffffffffu, acc[0], 1);
           const int h = (lane >> 1) & 15;
           if ((lane & 1) == 0) {
-            if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(tot * kBiasLog2e);
+            if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = bias16(tot);
             else proj[(long long)h * proj_plane + pidx[j]] = tot;
           }
         } else {
@@ -148,7 +156,7 @@ ln_rows_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, 
 #pragma unroll
           for (int h = 0; h < H; ++h)
             if (lane == (h & 31)) {
-              if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = __float2bfloat16(acc[h] * kBiasLog2e);
+              if (proj_bf16) proj_bf16[(long long)h * proj_plane + pidx[j]] = bias16(acc[h]);
               else proj[(long long)h * proj_plane + pidx[j]] = acc[h];
             }
         }
@@ -299,7 +307,7 @@ ln128_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y, lo
           const bool writer = (G == 16) ? true : ((l16 & 3) == 0);
           if (writer && valid_j) {
             const long long o = (long long)(hb + hsel) * proj_plane + pidx_of(prow_j);
-            if (proj_bf16) proj_bf16[o] = __float2bfloat16(acc[0] * kBiasLog2e);
+            if (proj_bf16) proj_bf16[o] = bias16(acc[0]);
             else proj[o] = acc[0];
           }
         }
@@ -418,7 +426,6 @@ ln128_tc_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y,
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
   constexpr uint32_t idesc = make_idesc(128, 16);
-  constexpr float kLog2e = 1.4426950408889634f;
   int buf = 0;
   uint32_t iter = 0;
   if ((long long)blockIdx.x < ntiles) fetch(blockIdx.x, 0);
@@ -501,7 +508,7 @@ ln128_tc_kernel(const bf16* __restrict__ x, long long ldx, bf16* __restrict__ y,
             const int h = hsel * 8 + j;
             if (h < H) {
               const float val = fmaf(st.y, __uint_as_float(d[j]) - st.x * colsum[h], colbias[h]);
-              proj_bf16[(long long)h * proj_plane + o] = __float2bfloat16(val * kLog2e);
+              proj_bf16[(long long)h * proj_plane + o] = bias16(val);
             }
           }
         }
