@@ -23,9 +23,9 @@
 //
 // The sweep exponentiates against the running reference exponent m_ref of the PREVIOUS halves,
 //     x = s * log2(e) - m_ref (fp32) -> fp16x2,  + bias' (fp16x2; bias' = bias * log2(e) as delivered),
-//     running max (fp16x2), ex2.approx.f16x2, row sum (fp16x2 partial sums), P as fp16,
-// and only looks at the maximum afterwards: if some row of the warp saw x > 8 (P > 256; fp16 would overflow beyond
-// 2^16), the warp takes the exact path -- fp32 row maximum of the half still held in registers, O (tensor memory),
+//     ex2.approx.f16x2, row sum (fp16x2 partial sums of 8 terms), P as fp16,
+// and only looks at the partial sums afterwards: if one of them exceeds 2^8 in some row of the warp (a P > 256, i.e.
+// x > 8, shows there; fp16 would overflow beyond 2^16), the warp takes the exact path -- fp32 row maximum of the half still held in registers, O (tensor memory),
 // the row sum and, in a block's second half, the stored first half of P rescaled, the sweep repeated.  The first half
 // of an item always takes the exact path.  With trained or random weights the repeat is rare afterwards.
 //
@@ -53,8 +53,12 @@ struct Attn3Args {
   int* status;
 };
 
-constexpr int A3_CTRL = 5;                      // TMA producer + four MMA issuers
-constexpr int A3_THREADS = (A3_CTRL + 16) * 32;  // + sixteen softmax warps
+constexpr int A3_CTRL = 8;                       // two control warpgroups: TMA producer, four MMA issuers, three idle warps
+constexpr int A3_THREADS = (A3_CTRL + 16) * 32;  // + four softmax warpgroups
+constexpr int A3_REGS_CTRL = 32, A3_REGS_SOFTMAX = 104;  // registers per thread after the re-balancing at kernel start
+#ifndef A3_STAGGER
+#define A3_STAGGER 600  // cycles between the first blocks of consecutive heads' softmax warpgroups (0: none)
+#endif
 constexpr uint32_t A3_Q = 32768;                 // [2 boxes][128 rows][64 columns]
 constexpr uint32_t A3_KV = 16384;                // [2 boxes][64 rows][64 columns]
 constexpr uint32_t A3_BT = 8192;                 // bias tile [128 queries][32 keys] fp16
@@ -99,6 +103,12 @@ __device__ __forceinline__ void tmem_st32_(uint32_t taddr, const uint32_t (&r)[3
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __global__ void __launch_bounds__(A3_THREADS, 1)
@@ -122,16 +132,18 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
   uint64_t* k_empty = bars + 4;    // [2] all four issuers have committed the block's logits
   uint64_t* v_full = bars + 6;     // [2]
   uint64_t* v_empty = bars + 8;    // [2] all four issuers have committed the block's P V product
-  uint64_t* s_full = bars + 10;    // [head] logits of a block are in TMEM
-  uint64_t* s_free = bars + 14;    // [head] the softmax warps hold the block's logits in registers (and have used up the
-                                   //        bias tile of its first half)
-  uint64_t* p_ready = bars + 18;   // [head] P of a block is in TMEM (and the bias tile of its second half is used up)
-  uint64_t* pv_done = bars + 22;   // [head] P V product of a block complete
-  uint64_t* b_full = bars + 26;    // [head][3] bias tile landed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 38);
+  uint64_t* sb_full = bars + 10;   // [head][block & 1] the logits of a block are in TMEM AND both of its bias tiles have
+                                   //        landed (three arrivals: the commit of the logits, the issuer's two expect-tx)
+  uint64_t* s_free = bars + 18;    // [head] the softmax warps hold the block's logits in registers
+  uint64_t* b_free = bars + 22;    // [head] the bias tile of a block's first half has been used up
+  uint64_t* p_ready = bars + 26;   // [head] P of a block is in TMEM (and the bias tile of its second half is used up)
+  uint64_t* pv_done = bars + 30;   // [head] P V product of a block complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // warp index and everything derived from it are the same in all lanes: the shuffle tells the compiler so, which keeps
+  // the issuers' descriptors and counters out of per-thread registers
+  const int warp = __shfl_sync(0xffffffffu, int(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
   const AbortCtx ab{cta_abort, p.status};
   const int KB = (p.S + 63) / 64;
   // Persistent CTA: work items (batch row, head group of 4, query tile), batch row slowest so that the K / V rows of
@@ -158,11 +170,12 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       mbar_init(&v_empty[s], 4);
     }
     for (int w = 0; w < 4; ++w) {
-      mbar_init(&s_full[w], 1);
+      mbar_init(&sb_full[w * 2], 3);
+      mbar_init(&sb_full[w * 2 + 1], 3);
       mbar_init(&s_free[w], 4);   // one elected lane per softmax warp
       mbar_init(&p_ready[w], 4);
+      mbar_init(&b_free[w], 4);
       mbar_init(&pv_done[w], 1);
-      for (int s = 0; s < A3_BS; ++s) mbar_init(&b_full[w * A3_BS + s], 1);
     }
     *cta_abort = 0;
     fence_barrier_init();
@@ -185,7 +198,12 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+
+  // Register re-balancing (whole warpgroups): the control warps run single threads with a handful of values, the
+  // softmax threads hold a block's 64 logits and 16 packed probabilities.
+  if (warp < A3_CTRL) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
+  else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A3_REGS_SOFTMAX));
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------- TMA producer
@@ -226,63 +244,72 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         }
       }
     }
-  } else if (warp < A3_CTRL) {
+  } else if (warp < 5) {
     // ------------------------------------------------------------------------------------------- MMA issuer of head w
-    if (lane == 0) {
+    // The whole warp runs this code with identical values in every lane (waits included), and one elected lane issues
+    // the tensor-core and TMA instructions: descriptors and counters are warp-uniform, built once outside the loop.
+    {
       const int w = warp - 1;
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc(128, 64);
       constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
                                                                   // projection buffer are written as fp16 by the GEMM
-      const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
       // head w lives in 64-column box w / 2, in the upper or lower 64 bytes of its 128-byte swizzled rows
-      const uint32_t q_addr = smem_u32(sQ) + uint32_t(w >> 1) * (A3_Q / 2) + uint32_t(w & 1) * 64u;
       const uint32_t k_off = uint32_t(w >> 1) * (A3_KV / 2) + uint32_t(w & 1) * 64u;
-      uint64_t* my_bfull = b_full + w * A3_BS;
-      uint8_t* my_bias = sBias + w * A3_BS * A3_BT;
+      const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
+      const uint64_t qd = make_sdesc(smem_u32(sQ) + uint32_t(w >> 1) * (A3_Q / 2) + uint32_t(w & 1) * 64u, 16, 1024);
+      const uint64_t kd0 = make_sdesc(smem_u32(sK) + k_off, 16, 1024);
+      const uint64_t mxd0 = make_sdesc_noswizzle(smem_u32(sMext), 128, 256);
+      const uint64_t vd0 = make_sdesc(smem_u32(sV) + k_off, 16384, 1024);  // V is N-major: 16 keys = 2048 B
+      const uint32_t d_s = tmem_base + w * 64, d_o = tmem_base + A3_TM_O + w * 32, a_p = tmem_base + A3_TM_P + w * 32;
+      uint64_t* my_sb = sb_full + w * 2;
+      const uint32_t my_bias = smem_u32(sBias) + w * A3_BS * A3_BT;
       bool okay = true;
       // next block whose logits are issued (one ahead of the softmax), tracked without divisions
       uint32_t aj = 0, ait = 0;
-      int akb = 0, aqt, ahg, ab_;
-      decode(0, aqt, ahg, ab_);
+      int akb = 0;
       auto issue_s = [&]() -> bool {
-        const uint32_t ks = aj & 1u, kpar = (aj >> 1) & 1u;
+        const uint32_t ks = aj & 1u;
         if (akb == 0 && !mbar_wait(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
-        if (!mbar_wait(&k_full[ks], kpar, ab, XF_ERR_WAIT_FULL)) return false;
+        if (!mbar_wait(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
         tc_fence_after();
-        const uint32_t d = tmem_base + w * 64;
-        const uint64_t qd = make_sdesc(q_addr, 16, 1024);
-        const uint64_t kd = make_sdesc(smem_u32(sK) + ks * A3_KV + k_off, 16, 1024);
-        const uint64_t mxd = make_sdesc_noswizzle(smem_u32(sMext) + ks * 2048, 128, 256);
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) umma_ss(d, qd + 2 * k, kd + 2 * k, idesc_s, k ? 1u : 0u);
-        umma_ss(d, e1d, mxd, idesc_s, 1u);
-        umma_commit(&s_full[w]);
-        umma_commit(&k_empty[ks]);
-        if (akb == KB - 1) umma_commit(q_empty);  // last use of this item's Q tile
+        if (leader) {
+          const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
+          umma_ss(d_s, qd, kd, idesc_s, 0u);
+          umma_ss(d_s, qd + 2, kd + 2, idesc_s, 1u);
+          umma_ss(d_s, e1d, mxd0 + uint64_t(ks * (2048 >> 4)), idesc_s, 1u);
+          umma_commit(&my_sb[ks]);  // ks = block & 1
+          umma_commit(&k_empty[ks]);
+          if (akb == KB - 1) umma_commit(q_empty);  // last use of this item's Q tile
+        }
         ++aj;
         if (++akb == KB) {
           akb = 0;
           ++ait;
-          decode(ait, aqt, ahg, ab_);
         }
         return true;
       };
       // next bias tile to fetch: half bi of the CTA's block sequence = (item, key block, half)
       uint32_t bi = 0, bslot = 0, bit = 0;
-      int bkb = 0, bh = 0, bqt, bhg, bb_;
+      int bkey = 0, bqt, bhg, bb_;
       decode(0, bqt, bhg, bb_);
+      const int key_end = KB * 64;
       auto issue_bias = [&]() {
-        mbar_arrive_expect_tx(&my_bfull[bslot], A3_BT);
-        tma_load_3d(my_bias + bslot * A3_BT, &tmb, &my_bfull[bslot], bkb * 64 + bh * 32, bqt * 128, bhg * 4 + w);
+        if (leader) {
+          uint64_t* bar = &my_sb[(bi >> 1) & 1u];  // the barrier of the block this half belongs to
+          mbar_arrive_expect_tx(bar, A3_BT);
+          asm volatile(
+              "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+              ::"r"(my_bias + bslot * A3_BT), "l"(&tmb), "r"(smem_u32(bar)), "r"(bkey), "r"(bqt * 128), "r"(bhg * 4 + w)
+              : "memory");
+        }
         ++bi;
         if (++bslot == A3_BS) bslot = 0;
-        if (++bh == 2) {
-          bh = 0;
-          if (++bkb == KB) {
-            bkb = 0;
-            ++bit;
-            decode(bit, bqt, bhg, bb_);
-          }
+        bkey += 32;
+        if (bkey == key_end) {
+          bkey = 0;
+          ++bit;
+          decode(bit, bqt, bhg, bb_);
         }
       };
       const uint32_t n_half = 2u * G;
@@ -291,30 +318,29 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       int kb = 0;  // key block of block g within its item
       for (uint32_t g = 0; g < G && okay; ++g) {
         const uint32_t par = g & 1u, vs = g & 1u, vpar = (g >> 1) & 1u;
-        // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1, and the bias tile of the
-        // first half of block g has been used up
+        // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1
         if (!mbar_wait(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (g + 1 < G && !issue_s()) break;
+        // the bias tile of the block's first half has been used up
+        if (!mbar_wait(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (bi < n_half) issue_bias();
         const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
         if (!mbar_wait(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
         tc_fence_after();
-        const uint32_t pt = tmem_base + A3_TM_P + w * 32;
-        const uint32_t vbase = smem_u32(sV) + vs * A3_KV + k_off;
-        const uint32_t d = tmem_base + A3_TM_O + w * 32;
+        if (leader) {
+          const uint64_t vd = vd0 + uint64_t(vs * (A3_KV >> 4));
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t bd = make_sdesc(vbase + ks * 2048, 16384, 1024);  // V is N-major: 16 keys = 2048 B
-          umma_ts(d, pt + ks * 8, bd, idesc_pv, (kb | ks) ? 1u : 0u);      // 16 keys = 8 columns of P; O accumulates
+          for (int ks = 0; ks < 4; ++ks)  // 16 keys = 2048 B of V = 8 columns of P; O accumulates over the item
+            umma_ts(d_o, a_p + ks * 8, vd + uint64_t(ks * (2048 >> 4)), idesc_pv, (kb | ks) ? 1u : 0u);
+          umma_commit(&pv_done[w]);
+          umma_commit(&v_empty[vs]);
         }
-        umma_commit(&pv_done[w]);
-        umma_commit(&v_empty[vs]);
         if (bi < n_half) issue_bias();
         if (++kb == KB) kb = 0;
       }
     }
-  } else {
+  } else if (warp >= A3_CTRL) {
     // ------------------------------------------------------------------------------------------- softmax warps
     const int w = (warp - A3_CTRL) >> 2;
     const int q4 = warp & 3;  // TMEM lane quarter this warp may access
@@ -325,10 +351,16 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
     const uint32_t p_addr = tmem_base + A3_TM_P + w * 32 + lane_addr;
     const uint32_t bsw = uint32_t(row >> 1) & 3u;  // 64-byte swizzle: 16-byte chunk index XOR (row / 2) % 4
     const uint8_t* my_bias = sBias + w * A3_BS * A3_BT + row * 64;
-    uint64_t* my_bfull = b_full + w * A3_BS;
+    uint64_t* my_sb = sb_full + w * 2;
     const uint32_t FULL = 0xffffffffu;
-    uint32_t g = 0, bslot = 0, bpar = 0;  // block number; bias ring position and phase
+    uint32_t g = 0, bslot = 0;  // block number; bias ring position
     bool okay = true;
+    if (A3_STAGGER > 0 && w > 0) {
+      // the four heads share each scheduler's exponential unit: start them a fraction of a block apart, so that one
+      // head's loads, stores and barrier round trips fall into the others' sweeps
+      const long long t0 = clock64();
+      while (clock64() - t0 < (long long)w * A3_STAGGER) {}
+    }
     for (uint32_t it = 0; it < my_items && okay; ++it) {
       int qt, hg, b;
       decode(it, qt, hg, b);
@@ -336,24 +368,32 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       const bool qvalid = qi < p.S;
       // m_ref: exponent offset in use (log2 units); it follows the running maximum lazily (see the file header).
       float m_ref = -3.0e38f, l_run = 0.f;
+      bool next_ready = false;  // probe of this block's barrier, made before the previous block's second sweep
       for (int kb = 0; kb < KB && okay; ++kb, ++g) {
-        const uint32_t par = g & 1u;
-        okay = __all_sync(FULL, mbar_wait(&s_full[w], par, ab, XF_ERR_WAIT_ATTN));
-        if (!okay) break;
-        tc_fence_after();
-#pragma unroll 1
-        for (int h = 0; h < 2 && okay; ++h) {
-          uint32_t r[32];
-          tmem_ld32(s_addr + h * 32, r);
-          const uint8_t* bt = my_bias + bslot * A3_BT;
-          okay = __all_sync(FULL, mbar_wait(&my_bfull[bslot], bpar, ab, XF_ERR_WAIT_ATTN));
-          tmem_ld_wait();
+        // ONE wait per block: the logits and both bias tiles.  A barrier round trip costs a few hundred cycles even when
+        // the phase is long complete, so it is probed a sweep ahead, and everything else is probed early and consumed late.
+        // (Fetching the next block's logits before this block's probabilities are published was measured: slower, the
+        // fence before the publication waits for the load.)
+        if (!__all_sync(FULL, next_ready)) {
+          okay = __all_sync(FULL, mbar_wait(&my_sb[g & 1u], (g >> 1) & 1u, ab, XF_ERR_WAIT_ATTN));
           if (!okay) break;
-          if (h == 1) {  // both halves of S(g) have been read: the issuer may overwrite the buffer
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free[w]);
-          }
+        }
+        tc_fence_after();
+        uint32_t r[64];
+        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        // has the previous block's P V product read P?  (needed before this block's first P store)
+        bool pv_ok = (g == 0) || mbar_test_wait(&pv_done[w], (g - 1) & 1u);
+        tmem_ld_wait();
+        // the whole block of logits is in registers: the issuer may overwrite the buffer with the next block's
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[w]);
+        next_ready = false;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint8_t* bt = my_bias + bslot * A3_BT;
+          if (h == 1) next_ready = (kb + 1 < KB) && mbar_test_wait(&my_sb[(g + 1) & 1u], ((g + 1) >> 1) & 1u);
           bool exact = (kb == 0 && h == 0);
           __half2 hs[4];
           uint32_t pk[16];
@@ -368,8 +408,8 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                   const float2 bf = __half22float2(*reinterpret_cast<const __half2*>(&bw[e]));
-                  mx0 = fmaxf(mx0, fmaf(__uint_as_float(r[c4 * 8 + 2 * e]), LOG2E, bf.x));
-                  mx1 = fmaxf(mx1, fmaf(__uint_as_float(r[c4 * 8 + 2 * e + 1]), LOG2E, bf.y));
+                  mx0 = fmaxf(mx0, fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e]), LOG2E, bf.x));
+                  mx1 = fmaxf(mx1, fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e + 1]), LOG2E, bf.y));
                 }
               }
               const float mx = fmaxf(mx0, mx1);
@@ -394,6 +434,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
                 }
                 if (h == 1) {  // the first half of this block's P is already stored: bring it to the new reference
                   uint32_t q[16];
+                  tmem_st_wait_();
                   tmem_ld16_(p_addr, q);
                   tmem_ld_wait();
                   const __half2 a2 = __float2half2_rn(alpha);
@@ -409,7 +450,6 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             }
             // the sweep: exponent, fp16x2 pack, bias, running max, exponential, row sum (8 keys per 16-byte bias read)
             const float nm = -m_ref;
-            __half2 hm = __float2half2_rn(-65504.f);
 #pragma unroll
             for (int e = 0; e < 4; ++e) hs[e] = __float2half2_rn(0.f);
 #pragma unroll
@@ -418,10 +458,9 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
               const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float x0 = fmaf(__uint_as_float(r[c4 * 8 + 2 * e]), LOG2E, nm);
-                const float x1 = fmaf(__uint_as_float(r[c4 * 8 + 2 * e + 1]), LOG2E, nm);
+                const float x0 = fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e]), LOG2E, nm);
+                const float x1 = fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e + 1]), LOG2E, nm);
                 const __half2 xh = __hadd2(__floats2half2_rn(x0, x1), *reinterpret_cast<const __half2*>(&bw[e]));
-                hm = __hmax2(hm, xh);
                 uint32_t ph;
                 asm("ex2.approx.f16x2 %0, %1;" : "=r"(ph) : "r"(*reinterpret_cast<const uint32_t*>(&xh)));
                 hs[e] = __hadd2(hs[e], *reinterpret_cast<const __half2*>(&ph));
@@ -429,9 +468,10 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
               }
             }
             if (exact) break;
-            const float2 bm = __half22float2(hm);
-            if (!__any_sync(FULL, fmaxf(bm.x, bm.y) > 8.f)) break;
-            exact = true;  // some row outgrew the reference: exact maximum, rescale, sweep again
+            // a probability above 2^8 (x > 8) shows in the partial sum that holds it (8 terms each; an overflow reads inf)
+            const float2 bm = __half22float2(__hmax2(__hmax2(hs[0], hs[1]), __hmax2(hs[2], hs[3])));
+            if (!__any_sync(FULL, fmaxf(bm.x, bm.y) > 256.f)) break;
+            exact = true;  // some row may have outgrown the reference: exact maximum, rescale if so, sweep again
           }
           if (!okay) break;
           float ls0 = 0.f, ls1 = 0.f;
@@ -442,15 +482,22 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             ls1 += f.y;
           }
           l_run += ls0 + ls1;
-          if (h == 0 && g > 0) {
-            // the P V product of the previous block must have read P before it is overwritten
-            okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
-            if (!okay) break;
+          if (h == 0) {
+            // the P V product of the previous block must have read P before it is overwritten (probed at the block's start)
+            if (!__all_sync(FULL, pv_ok)) pv_ok = mbar_test_wait(&pv_done[w], (g - 1) & 1u);  // a second look, a sweep later
+            if (!__all_sync(FULL, pv_ok)) {
+              okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
+              if (!okay) break;
+            }
             tc_fence_after();
+            tmem_st16_(p_addr, pk);  // completes behind the second half's sweep
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&b_free[w]);  // this half's bias tile has been read by the whole warp
+          } else {
+            tmem_st16_(p_addr + 16, pk);
+            tmem_st_wait_();
           }
-          tmem_st16_(p_addr + h * 16, pk);
-          if (++bslot == A3_BS) { bslot = 0; bpar ^= 1u; }
-          tmem_st_wait_();
+          if (++bslot == A3_BS) bslot = 0;
         }
         if (!okay) break;
         tc_fence_before();

@@ -148,15 +148,27 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!mbar_wait(&empty[stage], phase ^ 1u, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
           uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
-          tma_load_3d(sA, &tmA, &full[stage], kb * BK, a1, a2);
-          tma_load_3d(sA + Cfg::A_BYTES, &tmB, &full[stage], kb * BK, tn * BN, bb);
+          if (!p.mn_major) {
+            tma_load_3d(sA, &tmA, &full[stage], kb * BK, a1, a2);
+            tma_load_3d(sA + Cfg::A_BYTES, &tmB, &full[stage], kb * BK, tn * BN, bb);
+          } else {
+            // operands stored [k][m] / [k][n]: one [64 k][64 m] box (8 KB, 128-byte rows) per 64 rows of the tile
+#pragma unroll
+            for (int x = 0; x < BM / 64; ++x) tma_load_3d(sA + x * 8192, &tmA, &full[stage], a1 + x * 64, kb * BK, a2);
+#pragma unroll
+            for (int x = 0; x < BN / 64; ++x)
+              tma_load_3d(sA + Cfg::A_BYTES + x * 8192, &tmB, &full[stage], tn * BN + x * 64, kb * BK, bb);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(BM, BN);
+      // MN-major operands (rows of the smem tile are K indices): 64-element chunks along M / N are 8 KB apart, a step of
+      // 16 along K is 16 rows of 128 B
+      const uint32_t idesc = p.mn_major ? make_idesc(BM, BN, 1, 1) : make_idesc(BM, BN);
+      const uint32_t lbo = p.mn_major ? 8192u : 16u, kstep = p.mn_major ? 128u : 2u;
       uint32_t stage = 0, phase = 0, it = 0;
       bool okay = true;
       for (long long t = blockIdx.x; t < total && okay; t += gridDim.x, ++it) {
@@ -168,11 +180,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!mbar_wait(&full[stage], phase, ab, XF_ERR_WAIT_FULL)) { okay = false; break; }
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + stage * Cfg::STAGE_BYTES);
-          const uint64_t ad = make_sdesc(sA, 16, 1024);
-          const uint64_t bd = make_sdesc(sA + Cfg::A_BYTES, 16, 1024);
+          const uint64_t ad = make_sdesc(sA, lbo, 1024);
+          const uint64_t bd = make_sdesc(sA + Cfg::A_BYTES, lbo, 1024);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k)  // 16 bf16 = 32 B along K inside the swizzled row
-            umma_ss(d, ad + 2 * k, bd + 2 * k, idesc, (kb | k) ? 1u : 0u);
+          for (int k = 0; k < BK / 16; ++k)  // K-major: 16 bf16 = 32 B along K inside the swizzled row
+            umma_ss(d, ad + kstep * k, bd + kstep * k, idesc, (kb | k) ? 1u : 0u);
           umma_commit(&empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }

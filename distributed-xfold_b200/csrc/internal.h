@@ -74,6 +74,7 @@ struct GemmArgs {
   int a_row_mode = 0;  // 0: tile rows are consecutive rows of A; 1: tile rows step along dim 2, dim 1 fixed
   int a_dim1 = 1;      // row mode 1: extent of dim 1
   int b_batched = 0;
+  int mn_major = 0;    // operands are stored [k][m] and [k][n] (tensor maps: inner dim = m / n, boxes of 64 x 64)
   // PLAIN / SWIGLU / GATE_RESID output
   bf16* out = nullptr;
   long long ldo = 0, out_batch_stride = 0;

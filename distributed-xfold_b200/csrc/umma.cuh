@@ -23,6 +23,9 @@ enum : int {
   XF_ERR_WAIT_PEER = 106,      // a peer rank never published its ready flag
 };
 
+#ifndef XF_PARK_NS
+#define XF_PARK_NS 20000u  // suspend-time hint of a parked barrier wait
+#endif
 #ifndef XF_WAIT_CYCLES
 #define XF_WAIT_CYCLES (3000000000LL)  // ~1.5 s at 1.9 GHz
 #endif
@@ -102,15 +105,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   if (mbar_try_wait(bar, parity)) return true;
   if (*ab.cta_abort) return false;
   const long long t0 = clock64();
-  while (!mbar_try_wait_parked(bar, parity, 20000u)) {
-    if (*ab.cta_abort) return false;
-    if (clock64() - t0 > XF_WAIT_CYCLES) {
-      *ab.cta_abort = 1;
-      atomicCAS(ab.status, 0, code);
-      return false;
+  // The loop body is what a waiting warp feeds the scheduler it shares with working warps: keep it to the probe and a
+  // branch, and look at the abort flag and the clock only every 16th round.
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait_parked(bar, parity, XF_PARK_NS)) return true;
+    if ((spin & 15u) == 0) {
+      if (*ab.cta_abort) return false;
+      if (clock64() - t0 > XF_WAIT_CYCLES) {
+        *ab.cta_abort = 1;
+        atomicCAS(ab.status, 0, code);
+        return false;
+      }
     }
   }
-  return true;
 }
 
 // ------------------------------------------------------------------------------------
