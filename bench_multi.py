@@ -51,18 +51,16 @@ def _timed(fn, steps, dev, world):
 
 
 def exchange_bytes_per_block(sh) -> float:
-    """Bytes this rank sends over NVLink per Pairformer block: four distributed transposes, and per
-    TriangleMultiplication either the other ranks' share of a, b and the output rows (channel slices) or its rows of b
-    to every other rank (gather)."""
+    """Bytes this rank sends over NVLink per Pairformer block: two distributed transposes, per TriangleMultiplication the
+    other ranks' share of a, b and of the output rows (channel slices), and its rows of the two pair biases and of the
+    pair logits to every other rank."""
     n, p, r = sh.n, sh.world, sh.r
     ld = (n + 7) // 8 * 8
     away = (p - 1) / p
-    transposes = 4 * away * r * n * 128 * 2
-    if sh.channel_sharded:
-        trimul = 2 * away * (2 * r * 128 * ld * 2 + (128 // p) * n * ld * 2)
-    else:
-        trimul = 2 * (p - 1) * r * 128 * ld * 2
-    return transposes + trimul
+    transposes = 2 * away * r * n * 128 * 2
+    trimul = 2 * away * (2 * r * 128 * ld * 2 + (128 // p) * n * ld * 2)
+    bias = (p - 1) * (4 + 4 + 16) * r * ld * 2
+    return transposes + trimul + bias
 
 
 def run_multi(args, world, rank, local_rank):
@@ -82,20 +80,21 @@ def run_multi(args, world, rank, local_rank):
         del st
     z_full_h, s_h, pm_h, sm_h = O.make_inputs(3, n, pad_frac=0.1)
     sh = row_sharded.RowSharding(n)
-    stages = row_sharded.CudaStages()
-    peer = sh.enable_peer_exchange(dev)
+    trunk = row_sharded.ShardedTrunk(sh, dev)  # peer-mapped buffers + the library's shard context
+    stack = ops.PackedPairformerStack(packed)
     z_h = z_full_h[sh.rows].to(torch.bfloat16).contiguous().pin_memory()
     s_h = s_h.to(torch.bfloat16).pin_memory()
     z_out_h, s_out_h = torch.empty_like(z_h).pin_memory(), torch.empty_like(s_h).pin_memory()
     z0, s0 = z_h.to(dev), s_h.to(dev)
     pm, sm = pm_h.to(dev), sm_h.to(dev)
-    pmt = pm.t().contiguous()
-    state = {"z": torch.empty_like(z0), "s": torch.empty_like(s0)}
+    s_dev = torch.empty_like(s0)
 
     # ---- parity of the sharded path against the one-GPU path, in this very run -------------------------------
     # Every rank runs the first block on its row shard; rank 0 also runs it on the whole pair representation through
     # the one-GPU entry point and compares (relative Frobenius over unpadded positions).
-    zs, ss = row_sharded.pairformer_block(sh, stages, z0.clone(), s0.clone(), pm, pmt, sm, packed[0])
+    trunk.load(z0)
+    ss = s0.clone()
+    zs = trunk.run(ss, pm, sm, ops.PackedPairformerStack(packed[:1]))
     z_sharded = sh.gather_rows(zs.contiguous())
     ops.synchronize_and_check(local_rank)
     parity = None
@@ -115,26 +114,23 @@ def run_multi(args, world, rank, local_rank):
     del z_sharded, zs, ss, z_full_h
     torch.cuda.empty_cache()
 
-    def recycle():
-        state["z"], state["s"] = row_sharded.pairformer_stack(sh, stages, state["z"], state["s"], pm, pmt, sm, packed)
-
-    def step_resident():
-        state["z"] = z0.clone()
-        state["s"] = s0.clone()
-        recycle()
+    def step_resident():  # one C-ABI call per rank runs all blocks, exchanges included
+        trunk.load(z0)
+        s_dev.copy_(s0)
+        trunk.run(s_dev, pm, sm, stack)
 
     def step_e2e():
-        state["z"] = z_h.to(dev, non_blocking=True)
-        state["s"] = s_h.to(dev, non_blocking=True)
-        recycle()
-        z_out_h.copy_(state["z"], non_blocking=True)
-        s_out_h.copy_(state["s"], non_blocking=True)
+        trunk.shard_view().copy_(z_h, non_blocking=True)
+        s_dev.copy_(s_h, non_blocking=True)
+        out = trunk.run(s_dev, pm, sm, stack)
+        z_out_h.copy_(out, non_blocking=True)
+        s_out_h.copy_(s_dev, non_blocking=True)
 
     lib.xfold_profile_enable(ctx, 0)
     for _ in range(args.warmup):
         step_resident()
     ops.synchronize_and_check(local_rank)
-    assert torch.isfinite(state["z"].float()).all()
+    assert torch.isfinite(trunk.shard_view().float()).all()
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -178,7 +174,7 @@ def run_multi(args, world, rank, local_rank):
         exchange = {"bytes_sent_per_rank_per_step": xbytes, "nvlink_floor_ms": xbytes / (NVLINK_GBS * 1e9) * 1e3,
                     "peer_exchange_kernels_ms": xms, "nvlink_peak_gbs": NVLINK_GBS,
                     "frac_of_nvlink": None if not xms else xbytes / (xms * 1e-3) / 1e9 / NVLINK_GBS,
-                    "form": "channel slices (rows -> channels, product, rows back)" if sh.channel_sharded else "all-gather of b"}
+                    "form": "channel slices (rows -> channels, product, rows back), incoming product on the same planes"}
         kern_ms = sum(v["ms_per_step"] for v in per_kernel.values())
         line = {"metric": "pairformer_ms_per_recycle", "value": ms_step, "unit": "ms", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "ms_per_block": ms_step / nb,
@@ -190,7 +186,7 @@ def run_multi(args, world, rank, local_rank):
                 "model_tflops": flops_block(n) * nb / (ms_step * 1e-3) / 1e12,
                 "kernels_note": f"per-kernel CUDA-event times of rank 0 from a separate instrumented pass ({ms_prof:.1f} ms per step)",
                 "rank0_kernel_ms_per_step": kern_ms, "rank0_glue_ms_per_step": ms_prof - kern_ms,
-                "peer_memory_exchange": bool(peer), "kernels": per_kernel}
+                "peer_memory_exchange": True, "kernels": per_kernel}
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -40,6 +40,12 @@ class PairformerWeights(C.Structure):
                 ("single_transition", TransitionWeights)]
 
 
+class ShardDesc(C.Structure):
+    _fields_ = [("world", ci), ("rank", ci), ("n_tokens", ci), ("row_starts", C.POINTER(ci)),
+                ("zbuf0", C.POINTER(vp)), ("zbuf1", C.POINTER(vp)), ("plane_a", C.POINTER(vp)), ("plane_b", C.POINTER(vp)),
+                ("plane_o", C.POINTER(vp)), ("bias", C.POINTER(vp)), ("flags", C.POINTER(vp))]
+
+
 # name -> (restype, argtypes); every symbol include/xfold_b200.h declares
 SIGNATURES = {
     "xfold_ctx_create": (ci, [ci, C.POINTER(vp)]),
@@ -82,6 +88,12 @@ SIGNATURES = {
     "xfold_trimul_scatter_rows_fwd": (ci, [vp, vp, ci, ci, ci, ci, C.POINTER(vp), C.POINTER(ci), ci, vp]),
     "xfold_peer_allgather_fwd": (ci, [vp, vp, ll, ll, C.POINTER(vp), ci, vp]),
     "xfold_peer_barrier": (ci, [vp, C.POINTER(vp), ci, ci, ci, vp]),
+    "xfold_shard_ctx_create": (ci, [vp, C.POINTER(ShardDesc), C.POINTER(vp)]),
+    "xfold_shard_ctx_destroy": (None, [vp]),
+    "xfold_shard_workspace_bytes": (sz, [vp]),
+    "xfold_pairformer_stack_sharded_fwd": (ci, [vp, vp, ci, vp, vp, vp, C.POINTER(PairformerWeights), ci, vp, sz, vp,
+                                                C.POINTER(ci)]),
+    "xfold_trimul_contract_planes_incoming_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),
     "xfold_transition_static_max_bytes": (sz, []),
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),
     "xfold_pairformer_workspace_bytes": (sz, [ci]),

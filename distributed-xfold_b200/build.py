@@ -7,7 +7,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "gemm.cu", "simt.cu", "attention.cu", "attention3.cu", "peer.cu"]
+SOURCES = ["api.cu", "gemm.cu", "simt.cu", "attention.cu", "attention3.cu", "peer.cu", "sharded.cu"]
 LIB = os.path.join(HERE, "libxfold_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-Xcompiler", "-Wno-unused-function"]

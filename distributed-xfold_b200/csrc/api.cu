@@ -5,27 +5,9 @@
 #include <cstring>
 
 #include "internal.h"
+#include "stages.h"
 
 namespace xf {
-
-struct AttnArgs;
-int launch_ln_rows(Ctx* c, const bf16* x, long long ldx, bf16* y, long long ldy, long long rows, int C, const float* g,
-                   const float* b, float eps, int H, const float* pw, float* proj, long long plane, const bf16* msc,
-                   const bf16* msh, int mod_rows, cudaStream_t st, bf16* proj_bf16 = nullptr, int trav_inner = 0,
-                   int trav_outer = 0, int proj_pitch = 0);
-int launch_mext(Ctx* c, const float* mask, long long mask_ld, bf16* out, int B, int S, cudaStream_t st);
-int launch_bias_transpose(Ctx* c, const float* in, bf16* out, int H, int S, int ldq, cudaStream_t st);
-int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0, int k_col0,
-                      int v_col0, int g_col0, int heads, const bf16* biasT, int ldq, const bf16* mext, int mext_rows,
-                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st);
-int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_stride, int R, int N, bf16* out,
-                 const float* gamma, const float* beta, float eps, cudaStream_t st);
-int launch_swiglu(Ctx* c, const bf16* in, bf16* out, long long rows, int F, cudaStream_t st);
-int launch_maskb(Ctx* c, const float* mask, long long mask_ld, float* out, int B, int S, int ld, cudaStream_t st);
-int launch_attention_op(Ctx* c, int D, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0,
-                        int k_col0, int v_col0, int g_col0, int head_groups, const float* bias,
-                        long long bias_head_stride, int bias_ld, const float* maskb, int maskb_ld, bf16* out,
-                        long long out_seq_stride, long long out_batch_stride, cudaStream_t st);
 
 int fail(Ctx* c, int code, const char* fmt, ...) {
   if (c) {
@@ -75,20 +57,6 @@ bool make_tmap_bf16_3d(CUtensorMap* m, const void* base, uint64_t d0, uint64_t d
   return r == CUDA_SUCCESS;
 }
 
-static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-
-struct Carver {
-  uint8_t* base;
-  size_t off = 0, cap;
-  Carver(void* p, size_t n) : base(static_cast<uint8_t*>(p)), cap(n) {}
-  void* take(size_t bytes) {
-    off = align_up(off, 1024);
-    void* r = base ? base + off : nullptr;
-    off += bytes;
-    return r;
-  }
-  bool ok() const { return off <= cap; }
-};
 
 // ---------------------------------------------------------------------------------------------
 // generic linear layers on top of the GEMM kernel
@@ -182,12 +150,11 @@ static int batched_contract(Ctx* c, const bf16* a_, const bf16* b_, bf16* out, i
 // ---------------------------------------------------------------------------------------------
 // module-level operators
 // ---------------------------------------------------------------------------------------------
-static inline int pad8(int n) { return (n + 7) & ~7; }
 
 // a / b are stored "row-interleaved channel-major": element (row i, channel c, k) at (i * 128 + c) * ld + k.
 // A rank's rows are one contiguous block, so the all-gather of b over the row-shard group is a plain
 // concatenation, and the per-channel operand of the contraction is a strided 2-D slice for TMA.
-static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N, int transposed_store,
+int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N, int transposed_store,
                           const xfold_trimul_weights* w, bf16* x, bf16* a_out, bf16* b_out, bf16* g, long long chan_stride,
                           long long row_stride, cudaStream_t st) {
   const long long M = (long long)R * N;
@@ -226,9 +193,9 @@ static int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N
 
 // o[i][c][j] = sum_k a[i][c][k] * b[j][c][k]   (a: Ri rows, b: Nj rows, both [.][128][ld]; o: [Ri][128][ldo])
 // (chan, row) strides in elements: row-interleaved [rows][128][ld] has (ld, 128*ld); channel-major [128][rows][ld] has (rows*ld, ld)
-static int trimul_contract(Ctx* c, const bf16* a_, long long a_cs, long long a_rs, const bf16* b_, long long b_cs,
+int trimul_contract(Ctx* c, const bf16* a_, long long a_cs, long long a_rs, const bf16* b_, long long b_cs,
                            long long b_rs, int Ri, int Nj, int K, bf16* o, long long o_cs, long long o_rs, cudaStream_t st,
-                           int channels = 128) {
+                           int channels) {
   if (((a_cs | a_rs | b_cs | b_rs | o_cs | o_rs) & 7)) return fail(c, XFOLD_ERR_ARG, "contract: strides must be multiples of 8");
   CUtensorMap tA, tB;
   if (!make_tmap_bf16_3d(&tA, a_, K, Ri, channels, a_rs, a_cs, 64, 128, 1) ||
@@ -249,9 +216,36 @@ static int trimul_contract(Ctx* c, const bf16* a_, long long a_cs, long long a_r
   return launch_gemm(c, EPI_PLAIN, 256, tA, tB, a, st);
 }
 
+// The incoming-edges product on the SAME channel planes as the outgoing one ('ckj,cki->cij',
+// nn/d_triangle_multiplication.py:122-124): o[c][i][j] = sum_k at[c][k][i] * bt[c][k][j], both operands read with the
+// contraction index as their slow dimension (MN-major tensor-core operands), so no transposed copy of z, a or b is made.
+int trimul_contract_mn(Ctx* c, const bf16* at, long long at_cs, long long at_rs, const bf16* bt, long long bt_cs,
+                       long long bt_rs, int Mi, int Nj, int K, bf16* o, long long o_cs, long long o_rs, cudaStream_t st,
+                       int channels) {
+  if (((at_cs | at_rs | bt_cs | bt_rs | o_cs | o_rs) & 7)) return fail(c, XFOLD_ERR_ARG, "contract: strides must be multiples of 8");
+  CUtensorMap tA, tB;
+  if (!make_tmap_bf16_3d(&tA, at, Mi, K, channels, at_rs, at_cs, 64, 64, 1) ||
+      !make_tmap_bf16_3d(&tB, bt, Nj, K, channels, bt_rs, bt_cs, 64, 64, 1))
+    return fail(c, XFOLD_ERR_ARG, "contract: cannot encode tensor maps");
+  GemmArgs a;
+  a.M = Mi;
+  a.N = Nj;
+  a.K = K;
+  a.batches = channels;
+  a.b_batched = 1;
+  a.mn_major = 1;
+  a.tiles_m = (Mi + 127) / 128;
+  a.tiles_n = (Nj + 255) / 256;
+  a.out = o;
+  a.ldo = o_rs;
+  a.out_batch_stride = o_cs;
+  a.status = c->d_status;
+  return launch_gemm(c, EPI_PLAIN, 256, tA, tB, a, st);
+}
+
 // z (+)= Linear(LN_c(o)) * sigmoid(g); o: [R][128][ldo]; x: scratch [R*N][128]
-static int trimul_output(Ctx* c, const bf16* o, long long o_cs, long long o_rs, const bf16* g, int R, int N,
-                         const xfold_trimul_weights* w, bf16* x, bf16* z, cudaStream_t st, bf16* upd = nullptr) {
+int trimul_output(Ctx* c, const bf16* o, long long o_cs, long long o_rs, const bf16* g, int R, int N,
+                         const xfold_trimul_weights* w, bf16* x, bf16* z, cudaStream_t st, bf16* upd) {
   int rc = launch_cm_ln(c, o, o_cs, o_rs, R, N, x, w->ln_c_gamma, w->ln_c_beta, 1e-5f, st);
   if (rc) return rc;
   // upd given: write the update alone there and leave z untouched; else z += update
@@ -315,7 +309,7 @@ static TriAttnWs carve_triattn(void* ws, size_t cap, int R, int N) {
 // x = LN(z) for a block of R rows, plus the pair bias those rows contribute, bf16, query-major [h][q][k]:
 //   rows_are_keys == 0: the rows are QUERY rows:  bias[h * plane + row_local * pitch + y]      (row-major walk)
 //   rows_are_keys == 1: the rows are KEY rows x:  bias[h * plane + y * pitch + x_local]        (column-by-column walk)
-static int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weights* w, bf16* x, bf16* bias,
+int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weights* w, bf16* x, bf16* bias,
                         int pitch, long long plane, int rows_are_keys, cudaStream_t st) {
   const long long M = (long long)R * N;
   if (!rows_are_keys)
@@ -327,9 +321,9 @@ static int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn
 
 // z (+)= out_proj(gated attention(x)) for R batch rows (sequence length N); biasT: bf16 [4][N][ldq], [h][query][key].
 // transposed: the R x N token grid is stored [N][R] (sequence index outermost), used by the single-GPU ending node.
-static int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
+int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
                         int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st,
-                        bf16* upd = nullptr) {
+                        bf16* upd) {
   const long long M = (long long)R * N;
   // the v columns are stored as fp16: the attention kernel's P V product runs with fp16 operands
   int rc = linear_plain(c, x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, qkvg, 512, st, 256, 384);
@@ -356,8 +350,8 @@ static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose,
   return triattn_core(c, W.x, W.nbT, W.ldq, mask, N, N, N, transpose, w, W.qkvg, W.mext, z, st, upd);
 }
 
-static int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
-                          size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr) {
+int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
+                          size_t ws_bytes, cudaStream_t st, bf16* upd) {
   if (!x || !w || !w->w1_packed || !w->w2) return fail(c, XFOLD_ERR_ARG, "transition: null argument");
   if (rows <= 0) return XFOLD_OK;
   // before any size arithmetic or launch: row counts the kernels cannot index, or whose byte sizes would wrap
@@ -435,14 +429,14 @@ static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int
                              W.maskb, 0, out, Wd, (long long)S * Wd, st);
 }
 
-static size_t single_ws_bytes(int N) {
+size_t single_ws_bytes(int N) {
   return align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 512 * 2, 1024) + apb_ws(1, N, 16, 32, nullptr, nullptr) +
          align_up((size_t)N * 384 * 2, 1024) + align_up((size_t)N * 1536 * 2, 1024) + 16384;
 }
 
 // single += AttentionPairBias(single, pair logits) ; single += Transition(single)   (nn/d_pairformer.py:162-169)
 // plT: bf16 [16][N][ldq] pair logits, [h][query][key].
-static int single_update(Ctx* c, bf16* s, const bf16* plT, int ldq, const float* seq_mask, int N,
+int single_update(Ctx* c, bf16* s, const bf16* plT, int ldq, const float* seq_mask, int N,
                          const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, cudaStream_t st) {
   Carver cv(ws, ws_bytes);
   bf16* xn = (bf16*)cv.take((size_t)N * 384 * 2);

@@ -27,6 +27,7 @@
 // argument covers the plane buffers of the channel-sharded contraction, which are written once per
 // TriangleMultiplication with a distributed transpose, i.e. a barrier, between two of them.
 #include "internal.h"
+#include "stages.h"
 #include "umma.cuh"
 
 namespace xf {
@@ -134,6 +135,132 @@ __global__ void peer_barrier_kernel(FlagTable ft, int epoch, int* status) {
   } while (true);
 }
 
+// Strided block broadcast: block k (k < nblk) of `blk16` 16-byte vectors, read at src + k * src_stride16, is stored to
+// every rank's buffer at dst_off16 + k * dst_stride16.  The all-gather of per-head bias planes whose local rows are
+// QUERY rows: head h's rows [row0, row0 + R) are one contiguous block of the destination plane.
+__global__ void __launch_bounds__(256)
+block_broadcast2d_kernel(const uint4* __restrict__ src, int nblk, long long blk16, long long src_stride16,
+                         long long dst_off16, long long dst_stride16, PeerTable pt) {
+  const long long per_rank = (long long)nblk * blk16, total = per_rank * pt.world;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int q = int(idx / per_rank);
+    const long long r = idx - (long long)q * per_rank;
+    const int k = int(r / blk16);
+    const long long v = r - (long long)k * blk16;
+    reinterpret_cast<uint4*>(pt.ptr[q])[dst_off16 + k * dst_stride16 + v] = src[k * src_stride16 + v];
+  }
+}
+
+// Column-block broadcast: `rows` rows of `cols` 16-bit elements (row pitch src_pitch) go to columns [col0, col0 + cols)
+// of the same rows of every rank's buffer (row pitch dst_pitch).  The all-gather of bias planes whose local rows are
+// KEY rows (they are columns of the [head][query][key] planes).  One warp per (row, rank); 16-byte stores when the
+// alignment allows, element stores otherwise.
+__global__ void __launch_bounds__(256)
+cols_broadcast_kernel(const uint16_t* __restrict__ src, long long rows, int cols, int src_pitch, int col0, int dst_pitch,
+                      PeerTable pt) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5), total = rows * pt.world;
+  const bool vec = ((cols | src_pitch | col0 | dst_pitch) & 7) == 0;
+  for (long long wi = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); wi < total; wi += warps) {
+    const int q = int(wi / rows);
+    const long long r = wi - (long long)q * rows;
+    const uint16_t* s = src + r * src_pitch;
+    uint16_t* d = reinterpret_cast<uint16_t*>(pt.ptr[q]) + r * dst_pitch + col0;
+    if (vec) {
+      for (int v = lane; v < (cols >> 3); v += 32) reinterpret_cast<uint4*>(d)[v] = reinterpret_cast<const uint4*>(s)[v];
+    } else {
+      for (int e = lane; e < cols; e += 32) d[e] = s[e];
+    }
+  }
+}
+
+static PeerTable make_table(void* const* ptrs, const int* starts, int world, int fill) {
+  PeerTable pt;
+  pt.world = world;
+  for (int q = 0; q < MAX_PEERS; ++q) pt.ptr[q] = q < world ? ptrs[q] : nullptr;
+  for (int q = 0; q <= MAX_PEERS; ++q) pt.start[q] = starts ? (q <= world ? starts[q] : fill) : 0;
+  return pt;
+}
+
+int launch_transpose_scatter(Ctx* c, const bf16* z, int R, int N, int row0, void* const* dst, const int* col_starts,
+                             int world, cudaStream_t st) {
+  if (R <= 0 || N <= 0) return XFOLD_OK;
+  const PeerTable pt = make_table(dst, col_starts, world, N);
+  const long long total = (long long)R * N * 16;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)c->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, st);
+  transpose_scatter_kernel<<<(int)blocks, 256, 0, st>>>(z, R, N, row0, pt);
+  return check_launch(c, "transpose_scatter_kernel");
+}
+
+int launch_channel_scatter(Ctx* c, const bf16* a, const bf16* b, int R, int N, int ld, int row0, void* const* peer_a,
+                           void* const* peer_b, int world, cudaStream_t st) {
+  if (R <= 0 || N <= 0) return XFOLD_OK;
+  const PeerTable pa = make_table(peer_a, nullptr, world, 0), pb = make_table(peer_b, nullptr, world, 0);
+  const long long rows = (long long)R * 128 * 2;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)c->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, st);
+  channel_scatter_kernel<<<(int)blocks, 256, 0, st>>>(a, b, R, N, ld, row0, 128 / world, pa, pb);
+  return check_launch(c, "channel_scatter_kernel");
+}
+
+int launch_row_scatter(Ctx* c, const bf16* o, int channels, int chan0, int N, int ldo, void* const* peer_o,
+                       const int* row_starts, int world, cudaStream_t st) {
+  if (channels <= 0 || N <= 0) return XFOLD_OK;
+  const PeerTable pt = make_table(peer_o, row_starts, world, N);
+  const long long rows = (long long)channels * N;
+  long long blocks = (rows + 7) / 8;
+  const long long cap = (long long)c->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, st);
+  row_scatter_kernel<<<(int)blocks, 256, 0, st>>>(o, channels, N, ldo, chan0, pt);
+  return check_launch(c, "row_scatter_kernel");
+}
+
+int launch_block_broadcast2d(Ctx* c, const void* src, int nblk, long long blk_bytes, long long src_stride_bytes,
+                             long long dst_off_bytes, long long dst_stride_bytes, void* const* dst, int world,
+                             cudaStream_t st) {
+  if (nblk <= 0 || blk_bytes <= 0) return XFOLD_OK;
+  if ((blk_bytes | src_stride_bytes | dst_off_bytes | dst_stride_bytes | (long long)reinterpret_cast<uintptr_t>(src)) & 15)
+    return fail(c, XFOLD_ERR_ARG, "peer broadcast: blocks, strides and offsets must be multiples of 16 bytes");
+  const PeerTable pt = make_table(dst, nullptr, world, 0);
+  const long long total = (long long)nblk * (blk_bytes >> 4) * world;
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)c->sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, st);
+  block_broadcast2d_kernel<<<(int)blocks, 256, 0, st>>>((const uint4*)src, nblk, blk_bytes >> 4, src_stride_bytes >> 4,
+                                                        dst_off_bytes >> 4, dst_stride_bytes >> 4, pt);
+  return check_launch(c, "block_broadcast2d_kernel");
+}
+
+int launch_cols_broadcast(Ctx* c, const void* src, long long rows, int cols, int src_pitch, int col0, int dst_pitch,
+                          void* const* dst, int world, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return XFOLD_OK;
+  const PeerTable pt = make_table(dst, nullptr, world, 0);
+  long long blocks = (rows * world + 7) / 8;
+  const long long cap = (long long)c->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  ProfScope ps(c, XFOLD_K_PEER, st);
+  cols_broadcast_kernel<<<(int)blocks, 256, 0, st>>>((const uint16_t*)src, rows, cols, src_pitch, col0, dst_pitch, pt);
+  return check_launch(c, "cols_broadcast_kernel");
+}
+
+int launch_peer_barrier(Ctx* c, void* const* peer_flags, int me, int world, int epoch, cudaStream_t st) {
+  FlagTable ft;
+  ft.world = world;
+  ft.me = me;
+  for (int q = 0; q < MAX_PEERS; ++q) ft.flags[q] = q < world ? (int*)peer_flags[q] : nullptr;
+  ProfScope ps(c, XFOLD_K_PEER, st);
+  peer_barrier_kernel<<<1, 32, 0, st>>>(ft, epoch, c->d_status);
+  return check_launch(c, "peer_barrier_kernel");
+}
+
 }  // namespace xf
 
 using namespace xf;
@@ -145,18 +272,7 @@ int xfold_transpose_scatter_fwd(xfold_ctx* cx, const void* z, int R, int N, int 
   Ctx* c = reinterpret_cast<Ctx*>(cx);
   if (!c || !z || !peer_bufs || !col_starts) return XFOLD_ERR_ARG;
   if (world < 1 || world > MAX_PEERS) return fail(c, XFOLD_ERR_ARG, "transpose: 1 to %d ranks supported, got %d", MAX_PEERS, world);
-  if (R <= 0 || N <= 0) return XFOLD_OK;
-  PeerTable pt;
-  pt.world = world;
-  for (int q = 0; q < MAX_PEERS; ++q) pt.ptr[q] = q < world ? peer_bufs[q] : nullptr;
-  for (int q = 0; q <= MAX_PEERS; ++q) pt.start[q] = q <= world ? col_starts[q] : N;
-  const long long total = (long long)R * N * 16;
-  long long blocks = (total + 255) / 256;
-  const long long cap = (long long)c->sm_count * 16;
-  if (blocks > cap) blocks = cap;
-  ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
-  transpose_scatter_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)z, R, N, row0, pt);
-  return check_launch(c, "transpose_scatter_kernel");
+  return launch_transpose_scatter(c, (const bf16*)z, R, N, row0, peer_bufs, col_starts, world, (cudaStream_t)stream);
 }
 
 int xfold_trimul_scatter_channels_fwd(xfold_ctx* cx, const void* a, const void* b, int R, int N, int ld, int row0,
@@ -165,22 +281,7 @@ int xfold_trimul_scatter_channels_fwd(xfold_ctx* cx, const void* a, const void* 
   if (!c || !a || !b || !peer_a || !peer_b) return XFOLD_ERR_ARG;
   if (world < 1 || world > MAX_PEERS || 128 % world) return fail(c, XFOLD_ERR_ARG, "channel scatter: the rank count must divide 128 (1, 2, 4, 8), got %d", world);
   if (ld & 7) return fail(c, XFOLD_ERR_ARG, "channel scatter: ld must be a multiple of 8");
-  if (R <= 0 || N <= 0) return XFOLD_OK;
-  PeerTable pa, pb;
-  pa.world = pb.world = world;
-  for (int q = 0; q < MAX_PEERS; ++q) {
-    pa.ptr[q] = q < world ? peer_a[q] : nullptr;
-    pb.ptr[q] = q < world ? peer_b[q] : nullptr;
-  }
-  for (int q = 0; q <= MAX_PEERS; ++q) pa.start[q] = pb.start[q] = 0;
-  const long long rows = (long long)R * 128 * 2;
-  long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)c->sm_count * 8;
-  if (blocks > cap) blocks = cap;
-  ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
-  channel_scatter_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)a, (const bf16*)b, R, N, ld, row0,
-                                                                         128 / world, pa, pb);
-  return check_launch(c, "channel_scatter_kernel");
+  return launch_channel_scatter(c, (const bf16*)a, (const bf16*)b, R, N, ld, row0, peer_a, peer_b, world, (cudaStream_t)stream);
 }
 
 int xfold_trimul_scatter_rows_fwd(xfold_ctx* cx, const void* o, int channels, int chan0, int N, int ldo,
@@ -189,18 +290,7 @@ int xfold_trimul_scatter_rows_fwd(xfold_ctx* cx, const void* o, int channels, in
   if (!c || !o || !peer_o || !row_starts) return XFOLD_ERR_ARG;
   if (world < 1 || world > MAX_PEERS) return fail(c, XFOLD_ERR_ARG, "row scatter: 1 to %d ranks supported, got %d", MAX_PEERS, world);
   if ((ldo & 7) || chan0 < 0 || chan0 + channels > 128) return fail(c, XFOLD_ERR_ARG, "row scatter: bad channel range or ldo");
-  if (channels <= 0 || N <= 0) return XFOLD_OK;
-  PeerTable pt;
-  pt.world = world;
-  for (int q = 0; q < MAX_PEERS; ++q) pt.ptr[q] = q < world ? peer_o[q] : nullptr;
-  for (int q = 0; q <= MAX_PEERS; ++q) pt.start[q] = q <= world ? row_starts[q] : N;
-  const long long rows = (long long)channels * N;
-  long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)c->sm_count * 8;
-  if (blocks > cap) blocks = cap;
-  ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
-  row_scatter_kernel<<<(int)blocks, 256, 0, (cudaStream_t)stream>>>((const bf16*)o, channels, N, ldo, chan0, pt);
-  return check_launch(c, "row_scatter_kernel");
+  return launch_row_scatter(c, (const bf16*)o, channels, chan0, N, ldo, peer_o, row_starts, world, (cudaStream_t)stream);
 }
 
 int xfold_peer_allgather_fwd(xfold_ctx* cx, const void* src, long long bytes, long long offset_bytes, void* const* peer_dst,
@@ -228,13 +318,7 @@ int xfold_peer_barrier(xfold_ctx* cx, void* const* peer_flags, int me, int world
   Ctx* c = reinterpret_cast<Ctx*>(cx);
   if (!c || !peer_flags) return XFOLD_ERR_ARG;
   if (world < 1 || world > MAX_PEERS || me < 0 || me >= world) return fail(c, XFOLD_ERR_ARG, "peer barrier: bad rank %d / world %d", me, world);
-  FlagTable ft;
-  ft.world = world;
-  ft.me = me;
-  for (int q = 0; q < MAX_PEERS; ++q) ft.flags[q] = q < world ? (int*)peer_flags[q] : nullptr;
-  ProfScope ps(c, XFOLD_K_PEER, (cudaStream_t)stream);
-  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ft, epoch, c->d_status);
-  return check_launch(c, "peer_barrier_kernel");
+  return launch_peer_barrier(c, peer_flags, me, world, epoch, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -440,6 +440,22 @@ def stage_trimul_contract_planes(a: torch.Tensor, b: torch.Tensor, n: int) -> to
     return o
 
 
+def stage_trimul_contract_planes_incoming(a: torch.Tensor, b: torch.Tensor, n: int) -> torch.Tensor:
+    """The incoming-edges product on the same channel planes: o[c, i, j] = sum_k a[c, k, j] * b[c, k, i] over the first n
+    rows k; a, b [channels, n, ld] -> o [channels, n, pad8(n)].  Nothing is transposed: the tensor-core operands are
+    read MN-major."""
+    _need_cuda(a, b)
+    dev = _dev(a)
+    ch, nk, ld = a.shape
+    assert b.shape == a.shape and a.is_contiguous() and b.is_contiguous() and nk >= n
+    ldo = _pad8(n)
+    o = torch.empty(ch, n, ldo, dtype=BF16, device=a.device)
+    rc = load().xfold_trimul_contract_planes_incoming_fwd(ctx(dev), _ptr(a), _ptr(b), ch, nk, n, n, ld, _ptr(o), ldo,
+                                                          _stream(dev))
+    check(rc, dev, "xfold_trimul_contract_planes_incoming_fwd")
+    return o
+
+
 def stage_trimul_output(o: torch.Tensor, g: torch.Tensor, z: torch.Tensor, w: PackedTriMul) -> None:
     _need_cuda(o, g, z)
     dev = _dev(z)

@@ -279,6 +279,90 @@ class PeerExchange:
         return p["o"][: sh.r * 128 * o.shape[2]].view(sh.r, 128, o.shape[2])
 
 
+class ShardedTrunk:
+    """The row-sharded block / trunk as ONE C-ABI call per stack of blocks (``xfold_pairformer_stack_sharded_fwd``): this
+    class only sets up what that call needs -- the peer-mapped (symmetric-memory) buffers every rank's kernels store
+    into, handed to the library as a shard context -- and keeps the pair shard in one of those buffers between calls.
+    World sizes 2, 4 and 8 (the channel slices of the TriangleMultiplication need 128 % world == 0); for anything else,
+    and on the CPU, ``pairformer_block`` above composes the same stages with collectives."""
+
+    def __init__(self, sh: "RowSharding", device):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm
+        from . import _cabi
+        if sh.world not in (2, 4, 8):
+            raise ValueError("ShardedTrunk: 2, 4 or 8 ranks")
+        self.sh, self._cabi, self._C = sh, _cabi, C
+        self.device = torch.device(device)
+        self.dev = self.device.index
+        group = sh.group if sh.group is not None else dist.group.WORLD
+        n, world, rmax = sh.n, sh.world, max(sh.sizes)
+        ld = (n + 7) // 8 * 8
+        cq = 128 // world
+        self.ld = ld
+        self._keep = []
+
+        def shared(numel, dtype=torch.bfloat16, zero=False):
+            t = symm.empty(numel, dtype=dtype, device=self.device)
+            if zero:
+                t.zero_()
+            h = symm.rendezvous(t, group)
+            off = t.data_ptr() - int(h.buffer_ptrs[sh.rank])
+            self._keep.append((t, h))
+            return t, (C.c_void_p * world)(*[int(p) + off for p in h.buffer_ptrs])
+
+        self.zbuf = [None, None]
+        self.zbuf[0], z0p = shared(rmax * n * 128)
+        self.zbuf[1], z1p = shared(rmax * n * 128)
+        _, pa = shared(cq * n * ld, zero=ld != n)
+        _, pb = shared(cq * n * ld, zero=ld != n)
+        _, po = shared(rmax * 128 * ld, zero=ld != n)
+        _, bias = shared(16 * n * ld, zero=True)
+        _, flags = shared(8, dtype=torch.int32, zero=True)
+        starts = (C.c_int * (world + 1))(*([sl.start for sl in sh.slices] + [n]))
+        self._ptrs = (z0p, z1p, pa, pb, po, bias, flags, starts)
+        desc = _cabi.ShardDesc(world, sh.rank, n, starts, z0p, z1p, pa, pb, po, bias, flags)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=sh.group)  # every rank's flags are zero before anyone signals
+        lib = _cabi.load()
+        out = C.c_void_p()
+        _cabi.check(lib.xfold_shard_ctx_create(_cabi.ctx(self.dev), C.byref(desc), C.byref(out)), self.dev,
+                    "xfold_shard_ctx_create")
+        self.handle = out.value
+        self.ws = torch.empty(lib.xfold_shard_workspace_bytes(self.handle), dtype=torch.uint8, device=self.device)
+        self.slot = 0
+
+    def shard_view(self, slot: Optional[int] = None) -> torch.Tensor:
+        """This rank's rows [R, N, 128] inside the peer-mapped buffer that currently holds them."""
+        sh = self.sh
+        k = self.slot if slot is None else slot
+        return self.zbuf[k][: sh.r * sh.n * 128].view(sh.r, sh.n, 128)
+
+    def load(self, z_shard: torch.Tensor) -> None:
+        """Copies this rank's rows into the library's buffer (the one copy a caller with its own z tensor needs)."""
+        self.shard_view().copy_(z_shard)
+
+    def run(self, s: Optional[torch.Tensor], pair_mask: torch.Tensor, seq_mask: Optional[torch.Tensor], stack) -> torch.Tensor:
+        """Runs every block of ``stack`` (an ops.PackedPairformerStack) on the shard held in the buffer; returns the view of
+        the updated rows.  pair_mask: the full [N, N] float32 mask (replicated); s: bf16 [N, 384], updated in place."""
+        C, _cabi = self._C, self._cabi
+        lib = _cabi.load()
+        out = C.c_int(self.slot)
+        stream = torch.cuda.current_stream(self.dev).cuda_stream
+        rc = lib.xfold_pairformer_stack_sharded_fwd(_cabi.ctx(self.dev), self.handle, self.slot,
+                                                    None if s is None else s.data_ptr(), pair_mask.data_ptr(),
+                                                    None if seq_mask is None else seq_mask.data_ptr(), stack.c, len(stack),
+                                                    self.ws.data_ptr(), self.ws.numel(), stream, C.byref(out))
+        _cabi.check(rc, self.dev, "xfold_pairformer_stack_sharded_fwd")
+        self.slot = out.value
+        return self.shard_view()
+
+    def close(self) -> None:
+        if self.handle:
+            self._cabi.load().xfold_shard_ctx_destroy(self.handle)
+            self.handle = None
+
+
 class CudaStages:
     """Stage backend on the C ABI (sm_100a kernels)."""
 

@@ -281,6 +281,49 @@ int xfold_peer_allgather_fwd(xfold_ctx* ctx, const void* src, long long bytes, l
  * xfold_check_status as XFOLD_ERR_TIMEOUT.  Epochs must increase by one per call. */
 int xfold_peer_barrier(xfold_ctx* ctx, void* const* peer_flags, int me, int world, int epoch, void* stream);
 
+/* ---- the block on a row shard, exchanges included ---------------------------------------------------
+ * DistributePairformerBlock.forward for dp_size > 1 (nn/d_pairformer.py:119-156) and the trunk loop around it
+ * (d_alphafold3.py:242-244) as ONE call per stack of blocks: the stages above plus every exchange between them
+ * (operand planes and output rows of the TriangleMultiplication, the two distributed transposes, the broadcasts of
+ * the pair bias and the pair logits), all as this library's peer-memory kernels and bounded flag barriers on the
+ * caller's stream.  The pair representation stays sharded from the first block to the last; the incoming
+ * TriangleMultiplication runs on the same channel planes as the outgoing one with MN-major tensor-core operands, so
+ * a block needs two distributed transposes where the reference does two all-gathers of the whole pair representation.
+ *
+ * The context replaces the reference's process-group bookkeeping (init_dist_info, distribute_utils.py:83-99) for this
+ * path: rank, world size, the row partition (ShardInfo rule, distribute_utils.py:101-128) and, per rank, the peer-mapped
+ * addresses (CUDA IPC / symmetric memory, mapped into this process by the caller) of
+ *   zbuf0, zbuf1 : two pair-shard buffers, rmax * N * 128 bf16 each (rmax = largest row count of a rank);
+ *   plane_a, plane_b : (128 / world) * N * pad8(N) bf16, operand planes of the rank's channels;
+ *   plane_o : rmax * 128 * pad8(N) bf16, contraction output rows;
+ *   bias : 16 * N * pad8(N) 16-bit, pair bias / pair logits [head][query][key];
+ *   flags : 8 ints, zero before the first call, used by nothing else.
+ * world must be 2, 4 or 8.  Every rank makes the same sequence of calls.  On entry the rank's rows are in its own
+ * zbuf<z_slot>; on return they are in zbuf<*z_slot_out>.  s (bf16 [N][384], replicated) may be NULL. */
+typedef struct xfold_shard_ctx xfold_shard_ctx;
+typedef struct {
+  int world, rank, n_tokens;
+  const int* row_starts; /* world + 1 offsets */
+  void* const* zbuf0;
+  void* const* zbuf1;
+  void* const* plane_a;
+  void* const* plane_b;
+  void* const* plane_o;
+  void* const* bias;
+  void* const* flags;
+} xfold_shard_desc;
+int xfold_shard_ctx_create(xfold_ctx* ctx, const xfold_shard_desc* desc, xfold_shard_ctx** out);
+void xfold_shard_ctx_destroy(xfold_shard_ctx* sc);
+size_t xfold_shard_workspace_bytes(const xfold_shard_ctx* sc);
+int xfold_pairformer_stack_sharded_fwd(xfold_ctx* ctx, xfold_shard_ctx* sc, int z_slot, void* s, const float* pair_mask,
+                                       const float* seq_mask, const xfold_pairformer_weights* blocks, int num_blocks,
+                                       void* ws, size_t ws_bytes, void* stream, int* z_slot_out);
+/* The incoming-edges product of TriangleMultiplication ('ckj,cki->cij', nn/d_triangle_multiplication.py:122-124) on the
+ * channel planes of xfold_trimul_contract_planes_fwd: a, b [channels][Nk][ld] -> o[c][i][j] = sum_k a[c][k][j] * b[c][k][i],
+ * o [channels][Ni][ldo]; no transposed copy is made. */
+int xfold_trimul_contract_planes_incoming_fwd(xfold_ctx* ctx, const void* a, const void* b, int channels, int Nk, int Ni,
+                                              int Nj, int ld, void* o, int ldo, void* stream);
+
 /* ---- update-only variants ----------------------------------------------------------------------
  * The reference's module forwards return the update and the caller adds it (`pair += module(pair, ...)`,
  * nn/d_pairformer.py:122-146).  These write the update to `update` (same shape as z) and leave z untouched. */

@@ -95,3 +95,52 @@ def test_row_sharded_block_nccl_ranks(pkg, oracle, n, pad, use_peer, channel):
     mp.spawn(_rank_main, args=(world, find_free_port(), n, pad, use_peer, channel, ret), nprocs=world, join=True)
     assert relf(ret["z"][pm > 0], rz[pm > 0]) < 2e-2
     assert relf(ret["s"][sm > 0], rs[sm > 0]) < 2e-2
+
+
+def _trunk_rank_main(rank, world, port, n, pad, nblocks, ret):
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as ge
+    ge.load_package()
+    O = ge.load_oracle()
+    from distributed_xfold_b200 import ops, row_sharded
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(f"cuda:{rank}"))
+    st = O.make_pairformer_stack_state(700 + n, nblocks)
+    z, s, pm, sm = O.make_inputs(701 + n, n, pad_frac=pad)
+    stack = ops.PackedPairformerStack.from_state(st, nblocks, f"cuda:{rank}")
+    sh = row_sharded.RowSharding(n)
+    trunk = row_sharded.ShardedTrunk(sh, f"cuda:{rank}")
+    sd = s.to(BF).cuda().contiguous()
+    pmd, smd = pm.cuda().contiguous(), sm.cuda().contiguous()
+    for rep in range(2):   # the second pass starts from buffers and flags the first one left behind
+        trunk.load(z[sh.rows].to(BF).cuda())
+        sd.copy_(s.to(BF).cuda())
+        zs = trunk.run(sd, pmd, smd, stack)
+        ops.synchronize_and_check(rank)
+    full = sh.gather_rows(zs.contiguous())
+    if rank == 0:
+        ret["z"], ret["s"] = full.float().cpu(), sd.float().cpu()
+    dist.barrier()
+    trunk.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n,pad,nblocks", [(128, 0.0, 2), (131, 0.1, 2), (200, 0.1, 3)])
+def test_sharded_trunk_one_call(pkg, oracle, n, pad, nblocks):
+    """The whole stack of blocks on the row shards as ONE C-ABI call per rank (peer-memory exchanges and flag barriers
+    inside; the incoming TriangleMultiplication on untransposed planes) against the fp32 oracle's block loop."""
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two or more GPUs")
+    from distributed_xfold_b200.distribute_utils import find_free_port
+    st = {k: v.to(BF).float() for k, v in oracle.make_pairformer_stack_state(700 + n, nblocks).items()}
+    z, s, pm, sm = oracle.make_inputs(701 + n, n, pad_frac=pad)
+    rz, rs = z.to(BF).float(), s.to(BF).float()
+    with torch.no_grad():
+        for i in range(nblocks):
+            rz, rs = oracle.pairformer_block(st, f"trunk_pairformer.{i}.", rz, pm, rs, sm)
+    ret = mp.Manager().dict()
+    mp.spawn(_trunk_rank_main, args=(world, find_free_port(), n, pad, nblocks, ret), nprocs=world, join=True)
+    assert relf(ret["z"][pm > 0], rz[pm > 0]) < 2e-2
+    assert relf(ret["s"][sm > 0], rs[sm > 0]) < 2e-2

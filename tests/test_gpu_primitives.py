@@ -125,3 +125,26 @@ def test_layernorm_fused_projection_64(ops):
     ops.synchronize_and_check()
     ref = torch.nn.functional.layer_norm(x.float(), (C,), g, None, 1e-5)
     assert relf(proj.cpu(), (ref @ w.T).T) < 1e-4
+
+
+@pytest.mark.parametrize("ch,n", [(2, 64), (3, 200), (4, 333), (2, 520)])
+def test_contract_planes_incoming_mn_major(ops, ch, n):
+    """'ckj,cki->cij' (nn/d_triangle_multiplication.py:122-124) on untransposed channel planes: the GEMM reads both
+    operands with the contraction index as their slow dimension (MN-major tensor-core operands)."""
+    ld = (n + 7) // 8 * 8
+    a = torch.zeros(ch, n, ld, dtype=BF)
+    b = torch.zeros(ch, n, ld, dtype=BF)
+    a[:, :, :n] = rnd(ch, n, n, seed=11 + n)
+    b[:, :, :n] = rnd(ch, n, n, seed=12 + n)
+    # the pad columns are never read: poison them
+    a[:, :, n:] = float("nan")
+    b[:, :, n:] = float("nan")
+    o = ops.stage_trimul_contract_planes_incoming(a.cuda(), b.cuda(), n)
+    ops.synchronize_and_check()
+    ref = torch.einsum("ckj,cki->cij", a[:, :, :n].float(), b[:, :, :n].float())
+    assert relf(o[:, :, :n].float().cpu(), ref) < 4e-3
+    # and the outgoing product on the same planes, for the pair
+    o2 = ops.stage_trimul_contract_planes(a.nan_to_num(0.).cuda(), b.nan_to_num(0.).cuda(), n)
+    ops.synchronize_and_check()
+    ref2 = torch.einsum("cik,cjk->cij", a[:, :, :n].float(), b[:, :, :n].float())
+    assert relf(o2[:, :, :n].float().cpu(), ref2) < 4e-3
