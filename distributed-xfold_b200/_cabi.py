@@ -40,6 +40,26 @@ class PairformerWeights(C.Structure):
                 ("single_transition", TransitionWeights)]
 
 
+class TriMulWeightsF32(C.Structure):
+    _fields_ = [(n, vp) for n in ("ln_in_gamma", "ln_in_beta", "projection", "gate", "ln_c_gamma", "ln_c_beta",
+                                  "output_projection", "gating_linear")]
+
+
+class TriAttnWeightsF32(C.Structure):
+    _fields_ = [(n, vp) for n in ("ln_gamma", "ln_beta", "pair_bias_projection", "qkvg", "output_projection")]
+
+
+class TransitionWeightsF32(C.Structure):
+    _fields_ = [(n, vp) for n in ("ln_gamma", "ln_beta", "transition1", "transition2")]
+
+
+class PairformerWeightsF32(C.Structure):
+    _fields_ = [("tri_out", TriMulWeightsF32), ("tri_in", TriMulWeightsF32), ("att_start", TriAttnWeightsF32),
+                ("att_end", TriAttnWeightsF32), ("pair_transition", TransitionWeightsF32),
+                ("spl_ln_gamma", vp), ("spl_ln_beta", vp), ("spl_w", vp), ("sa_ln_gamma", vp), ("sa_ln_beta", vp),
+                ("sa_qkvg", vp), ("sa_qkvg_bias", vp), ("sa_out", vp), ("single_transition", TransitionWeightsF32)]
+
+
 class ShardDesc(C.Structure):
     _fields_ = [("world", ci), ("rank", ci), ("n_tokens", ci), ("row_starts", C.POINTER(ci)),
                 ("zbuf0", C.POINTER(vp)), ("zbuf1", C.POINTER(vp)), ("plane_a", C.POINTER(vp)), ("plane_b", C.POINTER(vp)),
@@ -94,6 +114,8 @@ SIGNATURES = {
     "xfold_pairformer_stack_sharded_fwd": (ci, [vp, vp, ci, vp, vp, vp, C.POINTER(PairformerWeights), ci, vp, sz, vp,
                                                 C.POINTER(ci)]),
     "xfold_trimul_contract_planes_incoming_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),
+    "xfold_pairformer_f32_workspace_bytes": (sz, [ci]),
+    "xfold_pairformer_stack_f32_fwd": (ci, [vp, vp, vp, vp, vp, ci, C.POINTER(PairformerWeightsF32), ci, vp, sz, vp]),
     "xfold_transition_static_max_bytes": (sz, []),
     "xfold_transition_static_fwd": (ci, [vp, vp, ll, ci, ci, C.POINTER(TransitionWeights), vp]),
     "xfold_pairformer_workspace_bytes": (sz, [ci]),

@@ -7,7 +7,9 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "gemm.cu", "simt.cu", "attention.cu", "attention3.cu", "peer.cu", "sharded.cu"]
+SOURCES = ["api.cu", "gemm.cu", "simt.cu", "attention.cu", "attention3.cu", "peer.cu", "sharded.cu", "fp32_validation.cu"]
+# the fp32 validation kernels want IEEE division, exact exponentials and denormals: no fast-math for that file
+NO_FAST_MATH = {"fp32_validation.cu"}
 LIB = os.path.join(HERE, "libxfold_b200.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall", "-Xcompiler", "-Wno-unused-function"]
@@ -29,7 +31,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     procs = []
     for s in SOURCES:
         o = os.path.join(CSRC, s.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, *os.environ.get("XFOLD_NVCC_EXTRA", "").split(), "-c", os.path.join(CSRC, s), "-o", o]
+        flags = [f for f in NVCC_FLAGS if not (s in NO_FAST_MATH and f == "--use_fast_math")]
+        cmd = [nvcc, *flags, *os.environ.get("XFOLD_NVCC_EXTRA", "").split(), "-c", os.path.join(CSRC, s), "-o", o]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -390,6 +390,82 @@ def pairformer_stack_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq
 
 
 # ---------------------------------------------------------------------------------------------
+# fp32 validation build: float32 weights in the reference's own layouts, float32 z and s
+# ---------------------------------------------------------------------------------------------
+class PackedPairformerBlockF32:
+    """Float32 weights of one block for ``xfold_pairformer_stack_f32_fwd``: nothing is re-laid-out except that the
+    four attention projections are stacked into one matrix."""
+
+    def __init__(self, state: State, prefix: str, device, with_single: bool = True):
+        self._keep = []
+
+        def f(name):
+            t = state.get(prefix + name)
+            if t is None:
+                return None
+            t = t.detach().to(device=device, dtype=torch.float32).contiguous()
+            self._keep.append(t)
+            return t.data_ptr()
+
+        def cat(names):
+            t = torch.cat([state[prefix + n].detach().float() for n in names], 0).to(device).contiguous()
+            self._keep.append(t)
+            return t.data_ptr()
+
+        def trimul(p):
+            return _cabi.TriMulWeightsF32(f(p + "left_norm_input.weight"), f(p + "left_norm_input.bias"), f(p + "projection.weight"),
+                                          f(p + "gate.weight"), f(p + "center_norm.weight"), f(p + "center_norm.bias"),
+                                          f(p + "output_projection.weight"), f(p + "gating_linear.weight"))
+
+        def triattn(p):
+            return _cabi.TriAttnWeightsF32(f(p + "act_norm.weight"), f(p + "act_norm.bias"), f(p + "pair_bias_projection.weight"),
+                                           cat([p + n + ".weight" for n in ("q_projection", "k_projection", "v_projection", "gating_query")]),
+                                           f(p + "output_projection.weight"))
+
+        def transition(p):
+            return _cabi.TransitionWeightsF32(f(p + "input_layer_norm.weight"), f(p + "input_layer_norm.bias"),
+                                              f(p + "transition1.weight"), f(p + "transition2.weight"))
+
+        w = _cabi.PairformerWeightsF32()
+        w.tri_out, w.tri_in = trimul("triangle_multiplication_outgoing."), trimul("triangle_multiplication_incoming.")
+        w.att_start, w.att_end = triattn("pair_attention1."), triattn("pair_attention2.")
+        w.pair_transition = transition("pair_transition.")
+        if with_single:
+            sa = "single_attention_."
+            w.spl_ln_gamma, w.spl_ln_beta = f("single_pair_logits_norm.weight"), f("single_pair_logits_norm.bias")
+            w.spl_w = f("single_pair_logits_projection.weight")
+            w.sa_ln_gamma, w.sa_ln_beta = f(sa + "adaptive_layernorm.layer_norm.weight"), f(sa + "adaptive_layernorm.layer_norm.bias")
+            w.sa_qkvg = cat([sa + n + ".weight" for n in ("q_projection", "k_projection", "v_projection", "gating_query")])
+            c = state[prefix + sa + "q_projection.weight"].shape[0]
+            b = torch.zeros(4 * c)
+            if prefix + sa + "q_projection.bias" in state:
+                b[:c] = state[prefix + sa + "q_projection.bias"].detach().float().cpu()
+            b = b.to(device)
+            self._keep.append(b)
+            w.sa_qkvg_bias = b.data_ptr()
+            w.sa_out = f(sa + "adaptive_zero_init.transition2.weight")
+            w.single_transition = transition("single_transition.")
+        self.c = w
+
+
+def pairformer_stack_f32_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq_mask, blocks):
+    """In place, float32: the blocks of ``blocks`` (PackedPairformerBlockF32) applied in order to z [N, N, 128] and s [N, 384]."""
+    _need_cuda(z, s, pair_mask, seq_mask)
+    assert z.dtype == torch.float32 and z.is_contiguous() and (s is None or (s.dtype == torch.float32 and s.is_contiguous()))
+    dev = _dev(z)
+    n = z.shape[0]
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_pairformer_f32_workspace_bytes(n))
+    pm = None if pair_mask is None else pair_mask.to(torch.float32).contiguous()
+    sm = None if seq_mask is None else seq_mask.to(torch.float32).contiguous()
+    arr = (_cabi.PairformerWeightsF32 * len(blocks))(*[b.c for b in blocks])
+    rc = lib.xfold_pairformer_stack_f32_fwd(ctx(dev), _ptr(z), _ptr(s), _ptr(pm), _ptr(sm), n, arr, len(blocks), _ptr(ws),
+                                            ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_pairformer_stack_f32_fwd")
+    return z, s
+
+
+# ---------------------------------------------------------------------------------------------
 # row-shard stages (the multi-GPU block composes these with collectives in between)
 # ---------------------------------------------------------------------------------------------
 def _pad8(n: int) -> int:

@@ -336,6 +336,37 @@ int xfold_triangle_attention_update_fwd(xfold_ctx* ctx, const void* z, void* upd
 int xfold_transition_update_fwd(xfold_ctx* ctx, const void* x, void* update, long long rows, int C, int F,
                                 const xfold_transition_weights* w, void* ws, size_t ws_bytes, void* stream);
 
+/* ---- fp32 validation build ------------------------------------------------------------------------
+ * The same block with float32 storage and float32 arithmetic (plain FMA products on the CUDA cores, exact
+ * exponentials), the counterpart of the float32 bodies the reference's ops dispatch to by dtype
+ * (csrc/Alpha_Attention.cpp:63-69, 85-91, 162-168).  It exists to check the path against the reference's float32
+ * results to 1e-4; it is not tuned.  Weights are float32 in the reference's OWN layouts (no packing):
+ * torch.nn.Linear weights [out][in]; `projection` / `gate` [256][128] with a / b rows interleaved as in the
+ * checkpoint (nn/d_triangle_multiplication.py:162-165); qkvg = q, k, v, gating_query weights stacked [4c][c]. */
+typedef struct {
+  const float *ln_in_gamma, *ln_in_beta, *projection, *gate, *ln_c_gamma, *ln_c_beta, *output_projection, *gating_linear;
+} xfold_trimul_weights_f32;
+typedef struct {
+  const float *ln_gamma, *ln_beta, *pair_bias_projection, *qkvg, *output_projection;
+} xfold_triattn_weights_f32;
+typedef struct {
+  const float *ln_gamma, *ln_beta, *transition1, *transition2;
+} xfold_transition_weights_f32;
+typedef struct {
+  xfold_trimul_weights_f32 tri_out, tri_in;
+  xfold_triattn_weights_f32 att_start, att_end;
+  xfold_transition_weights_f32 pair_transition;
+  const float *spl_ln_gamma, *spl_ln_beta, *spl_w; /* single path; spl_w NULL when the block has none */
+  const float *sa_ln_gamma, *sa_ln_beta, *sa_qkvg /* [1536][384] */, *sa_qkvg_bias /* [1536], zero past the q rows */,
+      *sa_out /* [384][384] adaptive_zero_init.transition2 */;
+  xfold_transition_weights_f32 single_transition;
+} xfold_pairformer_weights_f32;
+size_t xfold_pairformer_f32_workspace_bytes(int N);
+/* z float32 [N][N][128], s float32 [N][384] (or NULL), updated in place by `num_blocks` blocks. */
+int xfold_pairformer_stack_f32_fwd(xfold_ctx* ctx, float* z, float* s, const float* pair_mask, const float* seq_mask,
+                                   int N, const xfold_pairformer_weights_f32* blocks, int num_blocks, void* ws,
+                                   size_t ws_bytes, void* stream);
+
 /* ---- Transition for callers that cannot allocate device memory ------------------------------------
  * (This entry point has no counterpart in the reference.)
  * Same operation and result as xfold_transition_fwd, but the scratch (normalised input and SwiGLU
