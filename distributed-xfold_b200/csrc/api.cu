@@ -94,6 +94,12 @@ static int linear_plain(Ctx* c, const bf16* x, long long ldx, long long M, int K
   return gemm_rows(c, EPI_PLAIN, x, ldx, M, K, w, N, K, a, bn, st);
 }
 
+// for the translation units that compose operators out of plain projections
+int linear_plain_fwd(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N, const float* bias,
+                     const float* scale, bf16* out, long long ldo, cudaStream_t st) {
+  return linear_plain(c, x, ldx, M, K, w, N, bias, scale, out, ldo, st);
+}
+
 static int linear_gate_resid(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N,
                              const bf16* gate, long long ldg, int row_gate_mod, const bf16* resid, long long ldr,
                              bf16* out, long long ldo, cudaStream_t st) {
@@ -110,6 +116,25 @@ static int linear_gate_resid(Ctx* c, const bf16* x, long long ldx, long long M, 
   a.resid = resid;
   a.ldr = ldr;
   return gemm_rows(c, EPI_GATE_RESID, x, ldx, M, K, w, N, K, a, bn, st);
+}
+
+// The gated / residual projection in row chunks, with the caller's hook after each chunk's launch (see ChunkHook).
+static int linear_gate_resid_chunked(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N,
+                                     const bf16* resid, long long ldr, bf16* out, long long ldo, cudaStream_t st,
+                                     const ChunkHook* hook) {
+  if (!hook || hook->parts <= 1 || !hook->after)
+    return linear_gate_resid(c, x, ldx, M, K, w, N, nullptr, 0, 0, resid, ldr, out, ldo, st);
+  const long long unit = hook->unit > 0 ? hook->unit : 1;
+  long long per = (M + hook->parts - 1) / hook->parts;
+  per = (per + unit - 1) / unit * unit;
+  for (long long m0 = 0; m0 < M; m0 += per) {
+    const long long m = M - m0 < per ? M - m0 : per;
+    int rc = linear_gate_resid(c, x + m0 * ldx, ldx, m, K, w, N, nullptr, 0, 0, resid ? resid + m0 * ldr : nullptr, ldr,
+                               out + m0 * ldo, ldo, st);
+    if (rc) return rc;
+    if ((rc = hook->after(m0, m))) return rc;
+  }
+  return XFOLD_OK;
 }
 
 static int linear_swiglu(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* wp, int F, bf16* out,
@@ -323,7 +348,7 @@ int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weight
 // transposed: the R x N token grid is stored [N][R] (sequence index outermost), used by the single-GPU ending node.
 int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
                         int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st,
-                        bf16* upd) {
+                        bf16* upd, const ChunkHook* hook) {
   const long long M = (long long)R * N;
   // the v columns are stored as fp16: the attention kernel's P V product runs with fp16 operands
   int rc = linear_plain(c, x, 128, M, 128, (const bf16*)w->w_qkvg, 512, nullptr, w->qkvg_scale, qkvg, 512, st, 256, 384);
@@ -334,8 +359,8 @@ int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask,
   rc = launch_attention2(c, qkvg, 512, N, R, transposed, 0, 128, 256, 384, 4, biasT, ldq, mext, R, x, seq_stride,
                          batch_stride, st);
   if (rc) return rc;
-  return linear_gate_resid(c, x, 128, M, 128, (const bf16*)w->w_out, 128, nullptr, 0, 0, upd ? nullptr : z, 128,
-                           upd ? upd : z, 128, st);
+  return linear_gate_resid_chunked(c, x, 128, M, 128, (const bf16*)w->w_out, 128, upd ? nullptr : z, 128, upd ? upd : z, 128,
+                                   st, hook);
 }
 
 static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose, const xfold_triattn_weights* w, void* ws,
@@ -351,7 +376,7 @@ static int triattn_fwd(Ctx* c, bf16* z, const float* mask, int N, int transpose,
 }
 
 int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
-                          size_t ws_bytes, cudaStream_t st, bf16* upd) {
+                          size_t ws_bytes, cudaStream_t st, bf16* upd, const ChunkHook* hook) {
   if (!x || !w || !w->w1_packed || !w->w2) return fail(c, XFOLD_ERR_ARG, "transition: null argument");
   if (rows <= 0) return XFOLD_OK;
   // before any size arithmetic or launch: row counts the kernels cannot index, or whose byte sizes would wrap
@@ -365,7 +390,7 @@ int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_tr
   if (rc) return rc;
   rc = linear_swiglu(c, xn, C, rows, C, (const bf16*)w->w1_packed, F, h, F, st);
   if (rc) return rc;
-  return linear_gate_resid(c, h, F, rows, F, (const bf16*)w->w2, C, nullptr, 0, 0, upd ? nullptr : x, C, upd ? upd : x, C, st);
+  return linear_gate_resid_chunked(c, h, F, rows, F, (const bf16*)w->w2, C, upd ? nullptr : x, C, upd ? upd : x, C, st, hook);
 }
 
 struct ApbWs {

@@ -37,7 +37,29 @@ struct ShardCtx {
   void* bias[SH_MAX] = {nullptr};
   void* flags[SH_MAX] = {nullptr};
   int epoch = 0;  // flag barriers passed so far; every rank makes the same sequence of calls, so the counts agree
+  // Exchange kernels run on a second stream, chunk by chunk, while the producing GEMM works on its next chunk.
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev[8] = {nullptr};
+  int ev_next = 0;
+  int parts = 2;  // chunks per producing stage
 };
+
+// side stream waits for what `main` has launched so far
+static int fork_to_side(Ctx* c, ShardCtx* sc, cudaStream_t main) {
+  cudaEvent_t e = sc->ev[sc->ev_next];
+  sc->ev_next = (sc->ev_next + 1) & 7;
+  if (cudaEventRecord(e, main) != cudaSuccess || cudaStreamWaitEvent(sc->side, e, 0) != cudaSuccess)
+    return fail(c, XFOLD_ERR_LAUNCH, "sharded block: stream fork failed");
+  return XFOLD_OK;
+}
+// `main` waits for everything launched on the side stream so far
+static int join_side(Ctx* c, ShardCtx* sc, cudaStream_t main) {
+  cudaEvent_t e = sc->ev[sc->ev_next];
+  sc->ev_next = (sc->ev_next + 1) & 7;
+  if (cudaEventRecord(e, sc->side) != cudaSuccess || cudaStreamWaitEvent(main, e, 0) != cudaSuccess)
+    return fail(c, XFOLD_ERR_LAUNCH, "sharded block: stream join failed");
+  return XFOLD_OK;
+}
 
 struct ShardWs {
   bf16 *x, *g, *a, *b, *op, *qkvg, *mext, *bias_loc;
@@ -83,18 +105,39 @@ static int trimul_sharded(Ctx* c, ShardCtx* sc, bf16* z, const float* mask_rows,
                           const ShardWs& W, cudaStream_t st) {
   const int me = sc->rank, N = sc->n, ld = sc->ld, R = sc->start[me + 1] - sc->start[me], row0 = sc->start[me];
   int rc;
-  // a, b for this rank's rows, all channels: [R][128][ld]
-  if ((rc = trimul_project(c, z, mask_rows, R, N, 0, w, W.x, W.a, W.b, W.g, ld, (long long)128 * ld, st))) return rc;
-  if ((rc = launch_channel_scatter(c, W.a, W.b, R, N, ld, row0, sc->pa, sc->pb, sc->world, st))) return rc;
+  // a, b for this rank's rows, all channels: [R][128][ld]; the rows of a finished chunk leave for their planes on the
+  // second stream while the next chunk is projected
+  const int parts = sc->parts > 1 && R >= 2 * sc->parts ? sc->parts : 1;
+  const int rper = (R + parts - 1) / parts;
+  for (int r0 = 0; r0 < R; r0 += rper) {
+    const int rr = R - r0 < rper ? R - r0 : rper;
+    const long long t0 = (long long)r0 * N;
+    if ((rc = trimul_project(c, z + t0 * 128, mask_rows ? mask_rows + t0 : nullptr, rr, N, 0, w, W.x + t0 * 128,
+                             W.a + (long long)r0 * 128 * ld, W.b + (long long)r0 * 128 * ld, W.g + t0 * 128, ld,
+                             (long long)128 * ld, st))) return rc;
+    if ((rc = fork_to_side(c, sc, st))) return rc;
+    if ((rc = launch_channel_scatter(c, W.a + (long long)r0 * 128 * ld, W.b + (long long)r0 * 128 * ld, rr, N, ld, row0 + r0,
+                                     sc->pa, sc->pb, sc->world, sc->side))) return rc;
+  }
+  if ((rc = join_side(c, sc, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
   // this rank's channels, all rows: planes [cq][N][ld]
   const bf16* pa = (const bf16*)sc->pa[me];
   const bf16* pb = (const bf16*)sc->pb[me];
   const long long cs = (long long)N * ld;
-  if (outgoing) rc = trimul_contract(c, pa, cs, ld, pb, cs, ld, N, N, N, W.op, cs, ld, st, sc->cq);   // sum_k a[i][k] b[j][k]
-  else rc = trimul_contract_mn(c, pb, cs, ld, pa, cs, ld, N, N, N, W.op, cs, ld, st, sc->cq);         // sum_k b[k][i] a[k][j]
-  if (rc) return rc;
-  if ((rc = launch_row_scatter(c, W.op, sc->cq, me * sc->cq, N, ld, sc->po, sc->start, sc->world, st))) return rc;
+  // the product in groups of channels; a finished group's rows go back to their owners while the next group is computed
+  const int cparts = sc->parts > 1 && sc->cq >= 2 * sc->parts ? sc->parts : 1;
+  const int cper = (sc->cq + cparts - 1) / cparts;
+  for (int c0 = 0; c0 < sc->cq; c0 += cper) {
+    const int cc = sc->cq - c0 < cper ? sc->cq - c0 : cper;
+    const long long off = (long long)c0 * cs;
+    if (outgoing) rc = trimul_contract(c, pa + off, cs, ld, pb + off, cs, ld, N, N, N, W.op + off, cs, ld, st, cc);   // sum_k a[i][k] b[j][k]
+    else rc = trimul_contract_mn(c, pb + off, cs, ld, pa + off, cs, ld, N, N, N, W.op + off, cs, ld, st, cc);       // sum_k b[k][i] a[k][j]
+    if (rc) return rc;
+    if ((rc = fork_to_side(c, sc, st))) return rc;
+    if ((rc = launch_row_scatter(c, W.op + off, cc, me * sc->cq + c0, N, ld, sc->po, sc->start, sc->world, sc->side))) return rc;
+  }
+  if ((rc = join_side(c, sc, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
   return trimul_output(c, (const bf16*)sc->po[me], ld, (long long)128 * ld, W.g, R, N, w, W.x, z, st);
 }
@@ -114,10 +157,21 @@ static int block_sharded(Ctx* c, ShardCtx* sc, int* slot, bf16* s, const float* 
   if ((rc = launch_block_broadcast2d(c, W.bias_loc, 4, (long long)R * ld * 2, (long long)R * ld * 2, (long long)row0 * ld * 2,
                                      (long long)N * ld * 2, sc->bias, sc->world, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
-  if ((rc = triattn_core(c, W.x, bias, ld, mask_rows, N, R, N, 0, &w->att_start, W.qkvg, W.mext, z, st))) return rc;
-
-  // to the transposed shard: zT[j][i] = z[i][j]
-  if ((rc = launch_transpose_scatter(c, z, R, N, row0, sc->z[*slot ^ 1], sc->start, sc->world, st))) return rc;
+  // The attention's output projection runs in chunks of rows; the rows of a finished chunk are sent to the transposed
+  // shard (zT[j][i] = z[i][j], in the OTHER buffer of the rank that owns column j) on the second stream meanwhile.
+  ChunkHook to_t;
+  to_t.parts = sc->parts;
+  to_t.unit = N;
+  bf16* src = z;
+  int dst_slot = *slot ^ 1;
+  to_t.after = [&](long long m0, long long m) -> int {
+    int r = fork_to_side(c, sc, st);
+    if (r) return r;
+    return launch_transpose_scatter(c, src + m0 * 128, (int)(m / N), N, row0 + (int)(m0 / N), sc->z[dst_slot], sc->start,
+                                    sc->world, sc->side);
+  };
+  if ((rc = triattn_core(c, W.x, bias, ld, mask_rows, N, R, N, 0, &w->att_start, W.qkvg, W.mext, z, st, nullptr, &to_t))) return rc;
+  if ((rc = join_side(c, sc, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
   *slot ^= 1;
   bf16* zt = (bf16*)sc->z[*slot][me];
@@ -128,9 +182,11 @@ static int block_sharded(Ctx* c, ShardCtx* sc, int* slot, bf16* s, const float* 
   if ((rc = launch_cols_broadcast(c, W.bias_loc, (long long)4 * N, R, pitch_r, row0, ld, sc->bias, sc->world, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
   if ((rc = triattn_core(c, W.x, bias, ld, mask_rows, N, R, N, 0, &w->att_end, W.qkvg, W.mext, zt, st))) return rc;
-  if ((rc = transition_fwd(c, zt, (long long)R * N, 128, 512, &w->pair_transition, W.tr, W.tr_bytes, st))) return rc;
-  // and back
-  if ((rc = launch_transpose_scatter(c, zt, R, N, row0, sc->z[*slot ^ 1], sc->start, sc->world, st))) return rc;
+  // and back, overlapped with the Transition's second projection in the same way
+  src = zt;
+  dst_slot = *slot ^ 1;
+  if ((rc = transition_fwd(c, zt, (long long)R * N, 128, 512, &w->pair_transition, W.tr, W.tr_bytes, st, nullptr, &to_t))) return rc;
+  if ((rc = join_side(c, sc, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
   *slot ^= 1;
   if (!s || !w->spl_w) return XFOLD_OK;
@@ -151,6 +207,8 @@ using namespace xf;
 struct xfold_shard_ctx : public xf::ShardCtx {};
 
 extern "C" {
+
+void xfold_shard_ctx_destroy(xfold_shard_ctx* sc);
 
 int xfold_shard_ctx_create(xfold_ctx* cx, const xfold_shard_desc* d, xfold_shard_ctx** out) {
   Ctx* c = reinterpret_cast<Ctx*>(cx);
@@ -187,11 +245,23 @@ int xfold_shard_ctx_create(xfold_ctx* cx, const xfold_shard_desc* d, xfold_shard
     delete sc;
     return fail(c, XFOLD_ERR_ARG, "shard context: row offsets must rise from 0 to n_tokens and every peer pointer must be set");
   }
+  if (cudaStreamCreateWithFlags(&sc->side, cudaStreamNonBlocking) != cudaSuccess) ok = false;
+  for (int i = 0; i < 8 && ok; ++i) ok = cudaEventCreateWithFlags(&sc->ev[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
+    xfold_shard_ctx_destroy(sc);
+    return fail(c, XFOLD_ERR_DEVICE, "shard context: cannot create the exchange stream");
+  }
   *out = sc;
   return XFOLD_OK;
 }
 
-void xfold_shard_ctx_destroy(xfold_shard_ctx* sc) { delete sc; }
+void xfold_shard_ctx_destroy(xfold_shard_ctx* sc) {
+  if (!sc) return;
+  for (int i = 0; i < 8; ++i)
+    if (sc->ev[i]) cudaEventDestroy(sc->ev[i]);
+  if (sc->side) cudaStreamDestroy(sc->side);
+  delete sc;
+}
 
 size_t xfold_shard_workspace_bytes(const xfold_shard_ctx* sc) { return sc ? carve_shard(nullptr, 0, *sc).bytes : 0; }
 

@@ -2,6 +2,8 @@
 // api.cu (one GPU, and the row-shard stage entry points) and sharded.cu (the block on a row shard with the
 // exchanges between its stages).
 #pragma once
+#include <functional>
+
 #include "internal.h"
 
 namespace xf {
@@ -21,6 +23,15 @@ struct Carver {
     return r;
   }
   bool ok() const { return off <= cap; }
+};
+
+// Lets a caller overlap what follows an operator's LAST GEMM with that GEMM: the GEMM is issued in `parts` chunks of
+// rows (chunk boundaries at multiples of `unit` rows) and `after(first_row, rows)` is called once a chunk is launched.
+// The multi-GPU block uses it to send finished rows to their next owner on a second stream while the rest computes.
+struct ChunkHook {
+  int parts = 1;
+  long long unit = 1;
+  std::function<int(long long, long long)> after;
 };
 
 // ---- kernel launchers (simt.cu, attention*.cu) ----------------------------------------------------------
@@ -58,9 +69,9 @@ int triattn_bias(Ctx* c, const bf16* z, int R, int N, const xfold_triattn_weight
                  long long plane, int rows_are_keys, cudaStream_t st);
 int triattn_core(Ctx* c, bf16* x, const bf16* biasT, int ldq, const float* mask, long long mask_ld, int R, int N,
                  int transposed, const xfold_triattn_weights* w, bf16* qkvg, bf16* mext, bf16* z, cudaStream_t st,
-                 bf16* upd = nullptr);
+                 bf16* upd = nullptr, const ChunkHook* hook = nullptr);
 int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_transition_weights* w, void* ws,
-                   size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr);
+                   size_t ws_bytes, cudaStream_t st, bf16* upd = nullptr, const ChunkHook* hook = nullptr);
 size_t single_ws_bytes(int N);
 int single_update(Ctx* c, bf16* s, const bf16* plT, int ldq, const float* seq_mask, int N,
                   const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, cudaStream_t st);

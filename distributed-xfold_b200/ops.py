@@ -338,6 +338,45 @@ def attention_pair_bias_core(xn: torch.Tensor, w: PackedSelfAttention, pair_bias
     return out
 
 
+class PackedCrossAttention:
+    """Weights of the gated cross attention in the reference's op layout (query_w / gating_w [a, H, D], query_b [1, H, D],
+    key_w / value_w [m, H, D]; prototypes/Batched_DiffusionCrossAttention.py) stacked into the two projection matrices of
+    ``xfold_cross_attention_fwd``."""
+
+    def __init__(self, query_w, query_b, key_w, value_w, gating_w, device):
+        a, h, d = query_w.shape
+        m = key_w.shape[0]
+        self.H, self.D, self.Ca, self.Cm = h, d, a, m
+        flat = lambda w: w.detach().float().reshape(w.shape[0], h * d).T          # [H*D, in]
+        self.w_qg = _b16(torch.cat([flat(query_w), flat(gating_w)], 0), device)
+        self.w_kv = _b16(torch.cat([flat(key_w), flat(value_w)], 0), device)
+        bias = torch.zeros(2 * h * d)
+        if query_b is not None:
+            bias[: h * d] = query_b.detach().float().reshape(-1).cpu()
+        scale = torch.ones(2 * h * d)
+        scale[: h * d] = d ** -0.5
+        self.bias, self.scale = _f32(bias, device), _f32(scale, device)
+
+
+def cross_attention(q_data: torch.Tensor, m_data: torch.Tensor, batched_bias: torch.Tensor, w: PackedCrossAttention):
+    """q_data bf16 [B, S, a], m_data bf16 [B, K, m], batched_bias float32 [B, H, S, K] -> bf16 [B, S, H, D]."""
+    _need_cuda(q_data, m_data, batched_bias)
+    assert q_data.dtype == BF16 and m_data.dtype == BF16 and batched_bias.dtype == torch.float32
+    q_data, m_data, batched_bias = q_data.contiguous(), m_data.contiguous(), batched_bias.contiguous()
+    dev = _dev(q_data)
+    b, s_, _ = q_data.shape
+    k = m_data.shape[1]
+    assert tuple(batched_bias.shape) == (b, w.H, s_, k)
+    lib = load()
+    ws = _Workspace.get(dev, lib.xfold_cross_attention_workspace_bytes(b, s_, k, w.H, w.D))
+    out = torch.empty(b, s_, w.H, w.D, dtype=BF16, device=q_data.device)
+    rc = lib.xfold_cross_attention_fwd(ctx(dev), _ptr(q_data), _ptr(m_data), b, s_, k, w.Ca, w.Cm, w.H, w.D, _ptr(w.w_qg),
+                                       _ptr(w.bias), _ptr(w.scale), _ptr(w.w_kv), _ptr(batched_bias), _ptr(out), _ptr(ws),
+                                       ws.numel(), _stream(dev))
+    check(rc, dev, "xfold_cross_attention_fwd")
+    return out
+
+
 def pairformer_block_(z: torch.Tensor, s: Optional[torch.Tensor], pair_mask, seq_mask, w: PackedPairformerBlock):
     """In place: one Pairformer block on z bf16 [N, N, 128] and s bf16 [N, 384]."""
     _need_cuda(z, s, pair_mask, seq_mask)

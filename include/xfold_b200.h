@@ -170,6 +170,18 @@ int xfold_attention_pair_bias_core_fwd(xfold_ctx* ctx, const void* xn, int B, in
                                        const float* pair_bias, const float* mask, void* out, void* ws,
                                        size_t ws_bytes, void* stream);
 
+/* ---- gated cross attention (atom cross-attention core) ---------------------------------------------
+ * Replaces `_alpha_attention::batch_diffusion_cross_attention_forward` (csrc/Alpha_Attention.cpp:127-146, 201-204; spec
+ * class kernel_test/batch_diffusion_cross_attention.py:23-87): queries from q_data bf16 [B][S][Ca], keys and values from
+ * m_data bf16 [B][K][Cm], a float32 bias per batch entry [B][H][S][K], gate sigmoid(q_data gating_w), no output projection.
+ *   w_qg bf16 [2*H*D][Ca]: the query rows (head-major) then the gating rows; qg_bias / qg_scale float32 [2*H*D]
+ *   (query bias and D^-0.5 on the query rows, 0 / 1 on the gating rows); w_kv bf16 [2*H*D][Cm]: key rows then value rows.
+ * out: bf16 [B][S][H*D].  D in {16, 32, 64}. */
+size_t xfold_cross_attention_workspace_bytes(int B, int S, int K, int H, int D);
+int xfold_cross_attention_fwd(xfold_ctx* ctx, const void* q_data, const void* m_data, int B, int S, int K, int Ca, int Cm,
+                              int H, int D, const void* w_qg, const float* qg_bias, const float* qg_scale,
+                              const void* w_kv, const float* bias, void* out, void* ws, size_t ws_bytes, void* stream);
+
 /* ---- PairformerBlock --------------------------------------------------------------------------
  * DistributePairformerBlock.forward (nn/d_pairformer.py:99-171) for world size 1: both TriMuls,
  * both TriAttns, pair Transition, then pair-logit projection, single AttentionPairBias (16 heads x 24,

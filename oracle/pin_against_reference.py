@@ -180,6 +180,23 @@ def main():
         (SpecTransition,) = extract_classes(os.path.join(kt, "transition.py"), ["Transition"])
         (SelfAttention1,) = extract_classes(os.path.join(kt, "batch_diffusion_self_attention.py"), ["SelfAttention1"])
 
+        (CrossAttention,) = extract_classes(os.path.join(kt, "batch_diffusion_cross_attention.py"), ["CrossAttention"])
+        B, S, K, c, H = 5, 32, 128, 128, 4
+        g = torch.Generator().manual_seed(34)
+        net = CrossAttention(H, c, c, c)
+        ws = {}
+        for nme, p in net.named_parameters():
+            p.data = torch.randn(p.shape, generator=g) / 8
+            ws[nme] = p.data
+        qd = torch.randn(B, S, c, generator=g)
+        md = torch.randn(B, K, c, generator=g)
+        bb = torch.randn(B, H, S, K, generator=g)
+        bb = bb + 1e9 * ((torch.rand(B, 1, 1, K, generator=g) > 0.1).float() - 1)   # some keys masked out per batch entry
+        ref = net(qd, md, bb)
+        mine = O.cross_attention(qd, md, bb, ws["query_w"], ws["query_b"], ws["key_w"], ws["value_w"], ws["gating_w"])
+        record("spec/cross_attention", {"seed": 34, "B": B, "S": S, "K": K, "c": c, "H": H,
+                                        "checksum": checksum(qd, md, bb, *ws.values())}, ref, mine)
+
         B, S, c, H = 6, 20, 128, 4
         g = torch.Generator().manual_seed(31)
         net = GatingAttention(H, c, c, c)

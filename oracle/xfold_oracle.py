@@ -177,6 +177,24 @@ def gated_attention(q_data, bias, nonbatched_bias, query_w, key_w, value_w, gati
     return torch.cat(outs, 0)
 
 
+def cross_attention(q_data, m_data, batched_bias, query_w, query_b, key_w, value_w, gating_w):
+    """Spec class of the reference's kernel test for `batch_diffusion_cross_attention_forward`
+    (xsmm_kernels/kernel_test/batch_diffusion_cross_attention.py:23-87, CrossAttention.forward): the gated attention of
+    the atom cross-attention encoder / decoder (nn/d_diffusion_transformer.py:313-543), queries and keys from different
+    token sets, one bias per batch entry, no output projection.
+
+    q_data [B, S, a]; m_data [B, K, m]; batched_bias [B, H, S, K]; query_w / gating_w [a, H, D]; query_b [1, H, D];
+    key_w / value_w [m, H, D] -> [B, S, H, D]."""
+    D = query_w.shape[-1]
+    q = (torch.einsum("bqa,ahc->bqhc", q_data, query_w) + query_b) * D ** (-0.5)
+    k = torch.einsum("bka,ahc->bkhc", m_data, key_w)
+    v = torch.einsum("bka,ahc->bkhc", m_data, value_w)
+    logits = torch.einsum("bqhc,bkhc->bhqk", q, k) + batched_bias
+    w = torch.softmax(logits, dim=-1)
+    o = torch.einsum("bhqk,bkhc->bqhc", w, v)
+    return o * torch.sigmoid(torch.einsum("bqc,chv->bqhv", q_data, gating_w))
+
+
 def grid_self_attention(state: State, prefix: str, pair, mask, full_pair=None, transpose: bool = False,
                         num_head: int = 4, row_chunk: int = 0):
     """nn/d_attention.py:58-111 (DistributeGridSelfAttention.xsmm_forward / forward).

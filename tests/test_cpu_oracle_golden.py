@@ -81,3 +81,28 @@ def test_row_chunked_attention_equals_full(oracle):
         a = oracle.grid_self_attention(st, "", z, pm, z, False)
         b = oracle.grid_self_attention(st, "", z, pm, z, False, row_chunk=7)
     assert torch.allclose(a, b, atol=1e-5)
+
+
+def cross_attention_inputs(meta):
+    """The inputs the pin script drew for ``spec/cross_attention`` (parameters in the spec class's declaration order)."""
+    B, S, K, c, H = meta["B"], meta["S"], meta["K"], meta["c"], meta["H"]
+    D = c // H
+    g = torch.Generator().manual_seed(meta["seed"])
+    ws = {}
+    for name, shape in (("query_w", (c, H, D)), ("query_b", (1, H, D)), ("key_w", (c, H, D)), ("value_w", (c, H, D)),
+                        ("gating_w", (c, H, D))):
+        ws[name] = torch.randn(shape, generator=g) / 8
+    qd = torch.randn(B, S, c, generator=g)
+    md = torch.randn(B, K, c, generator=g)
+    bb = torch.randn(B, H, S, K, generator=g)
+    bb = bb + 1e9 * ((torch.rand(B, 1, 1, K, generator=g) > 0.1).float() - 1)
+    return qd, md, bb, ws
+
+
+def test_cross_attention_golden(oracle, golden):
+    """The reference's CrossAttention spec class (kernel_test/batch_diffusion_cross_attention.py:23-87)."""
+    meta, ref = golden["spec/cross_attention"]["meta"], golden["spec/cross_attention"]["out"][0]
+    qd, md, bb, ws = cross_attention_inputs(meta)
+    assert abs(checksum(qd, md, bb, *ws.values()) - meta["checksum"]) < 1e-6 * meta["checksum"], "input generation drifted"
+    out = oracle.cross_attention(qd, md, bb, ws["query_w"], ws["query_b"], ws["key_w"], ws["value_w"], ws["gating_w"])
+    assert range_rel(out, ref) < 2e-5

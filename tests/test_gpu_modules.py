@@ -215,3 +215,26 @@ def test_transition_with_affine_layernorm(ops, oracle):
     ops.transition_(xd, w)
     ops.synchronize_and_check()
     check_update(x, xd, ref)
+
+
+@pytest.mark.parametrize("case", ["golden", "ragged"])
+def test_cross_attention(ops, oracle, golden, case):
+    """Gated cross attention (the core of the atom cross-attention encoder / decoder) against the reference's spec-class
+    output, and on sizes that are no multiples of anything."""
+    if case == "golden":
+        from test_cpu_oracle_golden import cross_attention_inputs
+        qd, md, bb, ws = cross_attention_inputs(golden["spec/cross_attention"]["meta"])
+        ref = golden["spec/cross_attention"]["out"][0]
+    else:
+        g = torch.Generator().manual_seed(77)
+        B, S, K, c, H, D = 3, 19, 45, 128, 4, 32
+        ws = {n: torch.randn(shape, generator=g) / 8 for n, shape in (("query_w", (c, H, D)), ("query_b", (1, H, D)),
+              ("key_w", (c, H, D)), ("value_w", (c, H, D)), ("gating_w", (c, H, D)))}
+        qd, md, bb = torch.randn(B, S, c, generator=g), torch.randn(B, K, c, generator=g), torch.randn(B, H, S, K, generator=g)
+        rb = lambda t: t.to(BF).float()
+        ref = oracle.cross_attention(rb(qd), rb(md), bb, rb(ws["query_w"]), ws["query_b"], rb(ws["key_w"]), rb(ws["value_w"]),
+                                     rb(ws["gating_w"]))
+    w = ops.PackedCrossAttention(ws["query_w"], ws["query_b"], ws["key_w"], ws["value_w"], ws["gating_w"], "cuda")
+    out = ops.cross_attention(qd.to(BF).cuda(), md.to(BF).cuda(), bb.cuda(), w)
+    ops.synchronize_and_check()
+    assert relf(out.float().cpu(), ref) < 2e-2
