@@ -407,7 +407,7 @@ static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
   w.qkvg = (bf16*)cv->take((size_t)B * S * 4 * H * Dp * 2);
   w.maskb = (float*)cv->take((size_t)w.ldm * 4);
   w.biasT = (bf16*)cv->take((size_t)H * S * w.ldq * 2);
-  w.mext = (bf16*)cv->take((size_t)(w.ldm / 128) * 4096);
+  w.mext = (bf16*)cv->take((size_t)B * (w.ldm / 128) * 4096);  // room for one mask row per batch entry
   if (out) *out = w;
   return cv->off;
 }
@@ -415,19 +415,19 @@ static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
 // pair_bias: float32 [H][S][S], or, when pair_biasT is given, the same as bf16 [H][S][pad8(S)] (both [h][query][key])
 static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
                          const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
-                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st);
+                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st, long long mask_ld);
 static int apb_core_fwd(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
                         const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
-                        const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+                        const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st, long long mask_ld = 0) {
   c->attn_tag = XFOLD_K_APB_ATTENTION;  // accounted separately from the TriangleAttention launches
   const int rc = apb_core_fwd_(c, xn, B, S, C, H, Dp, w_qkvg, qkvg_bias, qkvg_scale, pair_bias, pair_biasT, mask, out, ws,
-                               ws_bytes, st);
+                               ws_bytes, st, mask_ld);
   c->attn_tag = XFOLD_K_ATTENTION;
   return rc;
 }
 static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int Dp, const bf16* w_qkvg,
                          const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias, const bf16* pair_biasT,
-                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st) {
+                         const float* mask, bf16* out, void* ws, size_t ws_bytes, cudaStream_t st, long long mask_ld) {
   if (!xn || !w_qkvg || !out || (!pair_bias && !pair_biasT)) return fail(c, XFOLD_ERR_ARG, "apb: null argument");
   if ((Dp != 32 && Dp != 64) || (H * Dp) % 128) return fail(c, XFOLD_ERR_ARG, "apb: H x Dp must be a multiple of 128 with Dp 32 or 64");
   Carver cv(ws, ws_bytes);
@@ -443,10 +443,13 @@ static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int
       if ((rc = launch_bias_transpose(c, pair_bias, W.biasT, H, S, W.ldq, st))) return rc;
       pair_biasT = W.biasT;
     }
-    if ((rc = launch_mext(c, mask, 0, W.mext, 1, S, st))) return rc;
-    return launch_attention2(c, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, H, pair_biasT, W.ldq, W.mext, 1, out, Wd,
+    // mask_ld > 0: one mask row per batch entry (the TriangleAttention op); else one row shared by all
+    const int mrows = (mask && mask_ld > 0) ? B : 1;
+    if ((rc = launch_mext(c, mask, mask_ld, W.mext, mrows, S, st))) return rc;
+    return launch_attention2(c, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, H, pair_biasT, W.ldq, W.mext, mrows, out, Wd,
                              (long long)S * Wd, st);
   }
+  if (mask && mask_ld > 0) return fail(c, XFOLD_ERR_ARG, "apb: a mask row per batch entry needs head dimension <= 32");
   if (!pair_bias) return fail(c, XFOLD_ERR_ARG, "apb: the 64-wide head kernel takes the float32 query-major bias");
   rc = launch_maskb(c, mask, 0, W.maskb, 1, S, W.ldm, st);
   if (rc) return rc;
@@ -675,6 +678,14 @@ int xfold_pairformer_block_fwd(xfold_ctx* c, void* z, void* s, const float* pair
                                const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream) {
   if (!c) return XFOLD_ERR_ARG;
   return pairformer_fwd(c, (bf16*)z, (bf16*)s, pair_mask, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+int xfold_gated_attention_core_fwd(xfold_ctx* c, const void* xn, int B, int S, int C, int H, int Dp, const void* w_qkvg,
+                                   const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias,
+                                   const float* mask, long long mask_ld, void* out, void* ws, size_t ws_bytes, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return apb_core_fwd(c, (const bf16*)xn, B, S, C, H, Dp, (const bf16*)w_qkvg, qkvg_bias, qkvg_scale, pair_bias, nullptr,
+                      mask, (bf16*)out, ws, ws_bytes, (cudaStream_t)stream, mask_ld);
 }
 
 int xfold_pairformer_stack_fwd(xfold_ctx* c, void* z, void* s, const float* pair_mask, const float* seq_mask, int N,

@@ -170,6 +170,14 @@ int xfold_attention_pair_bias_core_fwd(xfold_ctx* ctx, const void* xn, int B, in
                                        const float* pair_bias, const float* mask, void* out, void* ws,
                                        size_t ws_bytes, void* stream);
 
+/* The same core with one mask row per batch entry (mask float32, row b at mask + b * mask_ld; mask_ld = 0: one row for
+ * all), which is what `_alpha_attention::grid_self_attn_forward` takes as its `bias` [B, 1, 1, S]
+ * (csrc/Alpha_Attention.cpp:50-70); per-entry masks need Dp = 32. */
+int xfold_gated_attention_core_fwd(xfold_ctx* ctx, const void* xn, int B, int S, int C, int H, int Dp, const void* w_qkvg,
+                                   const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias,
+                                   const float* mask, long long mask_ld, void* out, void* ws, size_t ws_bytes,
+                                   void* stream);
+
 /* ---- gated cross attention (atom cross-attention core) ---------------------------------------------
  * Replaces `_alpha_attention::batch_diffusion_cross_attention_forward` (csrc/Alpha_Attention.cpp:127-146, 201-204; spec
  * class kernel_test/batch_diffusion_cross_attention.py:23-87): queries from q_data bf16 [B][S][Ca], keys and values from

@@ -1,0 +1,24 @@
+"""CPU: the Meta kernels registered for ``torch.ops._alpha_attention.*`` give the padded shapes of the reference's own
+shape-only kernels (xsmm_kernels/prototypes/register_fake_kernels.py:12-125): sequence axes rounded up to 64,
+TriangleMultiplication's two token axes to 32."""
+import torch
+
+
+def test_meta_shapes(pkg):
+    from distributed_xfold_b200 import op_library
+    op_library.register()
+    op_library.register()   # idempotent
+    ops = torch.ops._alpha_attention
+    m = lambda *s: torch.empty(*s, device="meta", dtype=torch.bfloat16)
+    f = lambda *s: torch.empty(*s, device="meta")
+    assert tuple(ops.traingle_multiplication_forward(m(70, 70, 128), f(70, 70, 1), 0, m(128), m(128), m(256, 128), m(256, 128),
+                                                     m(128), m(128), m(128, 128), m(128, 128)).shape) == (96, 96, 128)
+    assert tuple(ops.grid_self_attn_forward(m(5, 70, 128), f(5, 1, 1, 70), f(4, 70, 70), m(128, 4, 32), m(128, 4, 32),
+                                            m(128, 4, 32), m(128, 4, 32), m(4, 32, 128), 32, 32).shape) == (5, 128, 128)
+    assert tuple(ops.batch_diffusion_self_attention_forward(m(2, 64, 768), f(1, 1, 1, 64), f(16, 64, 64), m(768, 16, 48),
+                                                            f(1, 16, 48), m(768, 16, 48), m(768, 16, 48), m(768, 16, 48), 48,
+                                                            48).shape) == (2, 64, 16, 48)
+    assert tuple(ops.batch_diffusion_cross_attention_forward(m(9, 32, 128), m(9, 128, 128), f(9, 4, 32, 128), m(128, 4, 32),
+                                                             f(1, 4, 32), m(128, 4, 32), m(128, 4, 32), m(128, 4, 32), 32,
+                                                             32).shape) == (9, 64, 4, 32)
+    assert tuple(ops.transition_forward(m(3, 7, 128), m(128, 1024), f(512, 128), m(128), m(128)).shape) == (3, 7, 128)
