@@ -458,13 +458,15 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
               const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const float x0 = fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e]), LOG2E, nm);
-                const float x1 = fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e + 1]), LOG2E, nm);
-                const __half2 xh = __hadd2(__floats2half2_rn(x0, x1), *reinterpret_cast<const __half2*>(&bw[e]));
-                uint32_t ph;
-                asm("ex2.approx.f16x2 %0, %1;" : "=r"(ph) : "r"(*reinterpret_cast<const uint32_t*>(&xh)));
-                hs[e] = __hadd2(hs[e], *reinterpret_cast<const __half2*>(&ph));
-                pk[c4 * 4 + e] = ph;
+                float x0 = fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e]), LOG2E, nm);
+                float x1 = fmaf(__uint_as_float(r[h * 32 + c4 * 8 + 2 * e + 1]), LOG2E, nm);
+                // bias in with the mixed-precision add, fp32 exponentials, one pack per pair: fewer instructions (and a more
+                // accurate P) than packing first and exponentiating in fp16x2, which the hardware splits into halves anyway
+                asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tadd.rn.f32.f16 %0, lo, %0;\n\tadd.rn.f32.f16 %1, hi, %1;\n\t}"
+                : "+f"(x0), "+f"(x1) : "r"(bw[e]));
+                const __half2 ph2 = __floats2half2_rn(ex2f_(x0), ex2f_(x1));
+                hs[e] = __hadd2(hs[e], ph2);
+                pk[c4 * 4 + e] = *reinterpret_cast<const uint32_t*>(&ph2);
               }
             }
             if (exact) break;
