@@ -115,6 +115,8 @@ SIGNATURES = {
                                                 C.POINTER(ci)]),
     "xfold_trimul_contract_planes_incoming_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),
     "xfold_gated_attention_core_fwd": (ci, [vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, ll, vp, vp, sz, vp]),
+    "xfold_pair_bias_prepare_fwd": (ci, [vp, vp, ci, ci, vp, vp]),
+    "xfold_attention_pair_bias_core_prepared_fwd": (ci, [vp, vp, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "xfold_cross_attention_workspace_bytes": (sz, [ci, ci, ci, ci, ci]),
     "xfold_cross_attention_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
     "xfold_pairformer_f32_workspace_bytes": (sz, [ci]),

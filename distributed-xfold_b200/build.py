@@ -7,7 +7,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu", "gemm.cu", "simt.cu", "attention.cu", "attention3.cu", "peer.cu", "sharded.cu", "fp32_validation.cu", "cross_attention.cu"]
+SOURCES = ["api.cu", "gemm.cu", "simt.cu", "attention3.cu", "peer.cu", "sharded.cu", "fp32_validation.cu", "cross_attention.cu"]
 # the fp32 validation kernels want IEEE division, exact exponentials and denormals: no fast-math for that file
 NO_FAST_MATH = {"fp32_validation.cu"}
 LIB = os.path.join(HERE, "libxfold_b200.so")

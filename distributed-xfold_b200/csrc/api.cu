@@ -395,7 +395,6 @@ int transition_fwd(Ctx* c, bf16* x, long long rows, int C, int F, const xfold_tr
 
 struct ApbWs {
   bf16 *qkvg, *biasT, *mext;
-  float* maskb;
   int ldm, ldq;
 };
 static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
@@ -405,7 +404,6 @@ static size_t apb_ws(int B, int S, int H, int Dp, Carver* cv, ApbWs* out) {
   w.ldm = (S + 127) / 128 * 128;
   w.ldq = pad8(S);
   w.qkvg = (bf16*)cv->take((size_t)B * S * 4 * H * Dp * 2);
-  w.maskb = (float*)cv->take((size_t)w.ldm * 4);
   w.biasT = (bf16*)cv->take((size_t)H * S * w.ldq * 2);
   w.mext = (bf16*)cv->take((size_t)B * (w.ldm / 128) * 4096);  // room for one mask row per batch entry
   if (out) *out = w;
@@ -435,26 +433,18 @@ static int apb_core_fwd_(Ctx* c, const bf16* xn, int B, int S, int C, int H, int
   apb_ws(B, S, H, Dp, &cv, &W);
   if (!ws || !cv.ok()) return fail(c, XFOLD_ERR_ARG, "apb: workspace too small (%zu < %zu)", ws_bytes, cv.off);
   const int Wd = H * Dp;
-  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, W.qkvg, 4 * Wd, st,
-                        Dp == 32 ? 2 * Wd : 0, Dp == 32 ? 3 * Wd : 0);
+  // the v columns leave the projection as fp16: P and V are the fp16 operands of the P V product
+  int rc = linear_plain(c, xn, C, (long long)B * S, C, w_qkvg, 4 * Wd, qkvg_bias, qkvg_scale, W.qkvg, 4 * Wd, st, 2 * Wd, 3 * Wd);
   if (rc) return rc;
-  if (Dp == 32) {
-    if (!pair_biasT) {
-      if ((rc = launch_bias_transpose(c, pair_bias, W.biasT, H, S, W.ldq, st))) return rc;
-      pair_biasT = W.biasT;
-    }
-    // mask_ld > 0: one mask row per batch entry (the TriangleAttention op); else one row shared by all
-    const int mrows = (mask && mask_ld > 0) ? B : 1;
-    if ((rc = launch_mext(c, mask, mask_ld, W.mext, mrows, S, st))) return rc;
-    return launch_attention2(c, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, H, pair_biasT, W.ldq, W.mext, mrows, out, Wd,
-                             (long long)S * Wd, st);
+  if (!pair_biasT) {
+    if ((rc = launch_bias_transpose(c, pair_bias, W.biasT, H, S, W.ldq, st))) return rc;
+    pair_biasT = W.biasT;
   }
-  if (mask && mask_ld > 0) return fail(c, XFOLD_ERR_ARG, "apb: a mask row per batch entry needs head dimension <= 32");
-  if (!pair_bias) return fail(c, XFOLD_ERR_ARG, "apb: the 64-wide head kernel takes the float32 query-major bias");
-  rc = launch_maskb(c, mask, 0, W.maskb, 1, S, W.ldm, st);
-  if (rc) return rc;
-  return launch_attention_op(c, Dp, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, Wd / 128, pair_bias, (long long)S * S, S,
-                             W.maskb, 0, out, Wd, (long long)S * Wd, st);
+  // mask_ld > 0: one mask row per batch entry (the TriangleAttention op); else one row shared by all
+  const int mrows = (mask && mask_ld > 0) ? B : 1;
+  if ((rc = launch_mext(c, mask, mask_ld, W.mext, mrows, S, st))) return rc;
+  return launch_attention2(c, W.qkvg, 4 * Wd, S, B, 0, 0, Wd, 2 * Wd, 3 * Wd, H, pair_biasT, W.ldq, W.mext, mrows, out, Wd,
+                           (long long)S * Wd, st, Dp);
 }
 
 size_t single_ws_bytes(int N) {
@@ -678,6 +668,20 @@ int xfold_pairformer_block_fwd(xfold_ctx* c, void* z, void* s, const float* pair
                                const xfold_pairformer_weights* w, void* ws, size_t ws_bytes, void* stream) {
   if (!c) return XFOLD_ERR_ARG;
   return pairformer_fwd(c, (bf16*)z, (bf16*)s, pair_mask, seq_mask, N, w, ws, ws_bytes, (cudaStream_t)stream);
+}
+
+int xfold_pair_bias_prepare_fwd(xfold_ctx* c, const float* pair_bias, int H, int S, void* prepared, void* stream) {
+  if (!c || !pair_bias || !prepared) return XFOLD_ERR_ARG;
+  return launch_bias_transpose(c, pair_bias, (bf16*)prepared, H, S, pad8(S), (cudaStream_t)stream);
+}
+
+int xfold_attention_pair_bias_core_prepared_fwd(xfold_ctx* c, const void* xn, int B, int S, int C, int H, int Dp,
+                                                const void* w_qkvg, const float* qkvg_bias, const float* qkvg_scale,
+                                                const void* prepared_bias, const float* mask, void* out, void* ws,
+                                                size_t ws_bytes, void* stream) {
+  if (!c) return XFOLD_ERR_ARG;
+  return apb_core_fwd(c, (const bf16*)xn, B, S, C, H, Dp, (const bf16*)w_qkvg, qkvg_bias, qkvg_scale, nullptr,
+                      (const bf16*)prepared_bias, mask, (bf16*)out, ws, ws_bytes, (cudaStream_t)stream);
 }
 
 int xfold_gated_attention_core_fwd(xfold_ctx* c, const void* xn, int B, int S, int C, int H, int Dp, const void* w_qkvg,

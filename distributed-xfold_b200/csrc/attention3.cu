@@ -111,10 +111,14 @@ __device__ __forceinline__ bool elect_one() {
 }
 __device__ __forceinline__ void tmem_st_wait_() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-__global__ void __launch_bounds__(A3_THREADS, 1)
+// D = head dimension (32: four heads per work item, 64: two; either way an item's Q / K / V tiles are 128 columns wide)
+template <int D>
+__global__ void __launch_bounds__((A3_CTRL + 4 * (128 / D)) * 32, 1)
 attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CUtensorMap tmkv,
              const __grid_constant__ CUtensorMap tmb, const Attn3Args p) {
-  constexpr int D = 32;
+  static_assert(D == 32 || D == 64, "head dimension 32 or 64");
+  constexpr int NH = 128 / D;                       // heads per work item = softmax warpgroups
+  constexpr int THREADS = (A3_CTRL + 4 * NH) * 32;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -149,7 +153,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
   // Persistent CTA: work items (batch row, head group of 4, query tile), batch row slowest so that the K / V rows of
   // the ~gridDim.x items in flight stay in L2.  Every role walks the same sequence of blocks; block numbers (and with
   // them buffer indices and barrier phases) keep counting across items.
-  const int QT = (p.S + 127) / 128, HG = p.heads / 4;
+  const int QT = (p.S + 127) / 128, HG = p.heads / NH;
   const long long n_items = (long long)p.B * HG * QT;
   const uint32_t my_items = n_items > blockIdx.x ? uint32_t((n_items - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0u;
   const uint32_t G = my_items * uint32_t(KB);  // blocks this CTA processes in total (the launcher bounds items * KB to 2^30)
@@ -162,12 +166,12 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_empty, 4);
+    mbar_init(q_empty, NH);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 4);
+      mbar_init(&k_empty[s], NH);
       mbar_init(&v_full[s], 1);
-      mbar_init(&v_empty[s], 4);
+      mbar_init(&v_empty[s], NH);
     }
     for (int w = 0; w < 4; ++w) {
       mbar_init(&sb_full[w * 2], 3);
@@ -184,7 +188,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
     tma_prefetch_desc(&tmb);
   }
   // constant operand E1: un-swizzled [128][16] tile whose column 0 is all ones
-  for (uint32_t i = threadIdx.x; i < 4096 / 16; i += A3_THREADS) reinterpret_cast<uint4*>(sE1)[i] = make_uint4(0, 0, 0, 0);
+  for (uint32_t i = threadIdx.x; i < 4096 / 16; i += THREADS) reinterpret_cast<uint4*>(sE1)[i] = make_uint4(0, 0, 0, 0);
   __syncthreads();
   if (threadIdx.x < 128) {
     const uint32_t m = threadIdx.x;
@@ -202,8 +206,11 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
 
   // Register re-balancing (whole warpgroups): the control warps run single threads with a handful of values, the
   // softmax threads hold a block's 64 logits and 16 packed probabilities.
-  if (warp < A3_CTRL) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
-  else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A3_REGS_SOFTMAX));
+  // (With two heads per item the CTA has 512 threads and every thread 128 registers from the start.)
+  if constexpr (NH == 4) {
+    if (warp < A3_CTRL) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A3_REGS_SOFTMAX));
+  }
 
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------- TMA producer
@@ -244,7 +251,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         }
       }
     }
-  } else if (warp < 5) {
+  } else if (warp <= NH) {
     // ------------------------------------------------------------------------------------------- MMA issuer of head w
     // The whole warp runs this code with identical values in every lane (waits included), and one elected lane issues
     // the tensor-core and TMA instructions: descriptors and counters are warp-uniform, built once outside the loop.
@@ -254,14 +261,16 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       constexpr uint32_t idesc_s = make_idesc(128, 64);
       constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
                                                                   // projection buffer are written as fp16 by the GEMM
-      // head w lives in 64-column box w / 2, in the upper or lower 64 bytes of its 128-byte swizzled rows
-      const uint32_t k_off = uint32_t(w >> 1) * (A3_KV / 2) + uint32_t(w & 1) * 64u;
+      // D = 32: head w lives in 64-column box w / 2, in the upper or lower 64 bytes of its 128-byte swizzled rows;
+      // D = 64: head w is box w
+      const uint32_t box = D == 32 ? uint32_t(w >> 1) : uint32_t(w), in_row = D == 32 ? uint32_t(w & 1) * 64u : 0u;
+      const uint32_t k_off = box * (A3_KV / 2) + in_row;
       const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
-      const uint64_t qd = make_sdesc(smem_u32(sQ) + uint32_t(w >> 1) * (A3_Q / 2) + uint32_t(w & 1) * 64u, 16, 1024);
+      const uint64_t qd = make_sdesc(smem_u32(sQ) + box * (A3_Q / 2) + in_row, 16, 1024);
       const uint64_t kd0 = make_sdesc(smem_u32(sK) + k_off, 16, 1024);
       const uint64_t mxd0 = make_sdesc_noswizzle(smem_u32(sMext), 128, 256);
       const uint64_t vd0 = make_sdesc(smem_u32(sV) + k_off, 16384, 1024);  // V is N-major: 16 keys = 2048 B
-      const uint32_t d_s = tmem_base + w * 64, d_o = tmem_base + A3_TM_O + w * 32, a_p = tmem_base + A3_TM_P + w * 32;
+      const uint32_t d_s = tmem_base + w * 64, d_o = tmem_base + A3_TM_O + w * D, a_p = tmem_base + A3_TM_P + w * 32;
       uint64_t* my_sb = sb_full + w * 2;
       const uint32_t my_bias = smem_u32(sBias) + w * A3_BS * A3_BT;
       bool okay = true;
@@ -275,8 +284,9 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         tc_fence_after();
         if (leader) {
           const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
-          umma_ss(d_s, qd, kd, idesc_s, 0u);
-          umma_ss(d_s, qd + 2, kd + 2, idesc_s, 1u);
+#pragma unroll
+          for (int j = 0; j < D / 16; ++j)  // 16 head-dimension columns = 32 B inside the swizzled row
+            umma_ss(d_s, qd + uint64_t(2 * j), kd + uint64_t(2 * j), idesc_s, j ? 1u : 0u);
           umma_ss(d_s, e1d, mxd0 + uint64_t(ks * (2048 >> 4)), idesc_s, 1u);
           umma_commit(&my_sb[ks]);  // ks = block & 1
           umma_commit(&k_empty[ks]);
@@ -300,7 +310,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           mbar_arrive_expect_tx(bar, A3_BT);
           asm volatile(
               "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-              ::"r"(my_bias + bslot * A3_BT), "l"(&tmb), "r"(smem_u32(bar)), "r"(bkey), "r"(bqt * 128), "r"(bhg * 4 + w)
+              ::"r"(my_bias + bslot * A3_BT), "l"(&tmb), "r"(smem_u32(bar)), "r"(bkey), "r"(bqt * 128), "r"(bhg * NH + w)
               : "memory");
         }
         ++bi;
@@ -347,7 +357,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
     const int row = q4 * 32 + lane;
     const uint32_t lane_addr = uint32_t(q4 * 32) << 16;
     const uint32_t s_addr = tmem_base + w * 64 + lane_addr;
-    const uint32_t o_addr = tmem_base + A3_TM_O + w * 32 + lane_addr;
+    const uint32_t o_addr = tmem_base + A3_TM_O + w * D + lane_addr;
     const uint32_t p_addr = tmem_base + A3_TM_P + w * 32 + lane_addr;
     const uint32_t bsw = uint32_t(row >> 1) & 3u;  // 64-byte swizzle: 16-byte chunk index XOR (row / 2) % 4
     const uint8_t* my_bias = sBias + w * A3_BS * A3_BT + row * 64;
@@ -424,12 +434,15 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
                   okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
                   if (!okay) break;
                   tc_fence_after();
-                  uint32_t o[32];
-                  tmem_ld32(o_addr, o);
-                  tmem_ld_wait();
+#pragma unroll 1
+                  for (int oc = 0; oc < D; oc += 32) {
+                    uint32_t o[32];
+                    tmem_ld32(o_addr + oc, o);
+                    tmem_ld_wait();
 #pragma unroll
-                  for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                  tmem_st32_(o_addr, o);
+                    for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                    tmem_st32_(o_addr + oc, o);
+                  }
                   tmem_st_wait_();
                 }
                 if (h == 1) {  // the first half of this block's P is already stored: bring it to the new reference
@@ -511,17 +524,19 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
       if (!okay) break;
       tc_fence_after();
+      const float inv = __fdividef(1.f, l_run);
+#pragma unroll 1
+      for (int oc = 0; oc < D; oc += 32) {
       uint32_t o[32];
-      tmem_ld32(o_addr, o);
+      tmem_ld32(o_addr + oc, o);
       tmem_ld_wait();
-      tc_fence_before();
+      if (oc + 32 == D) tc_fence_before();
       if (qvalid) {
-        const int col = hg * 128 + w * D;
-        const float inv = __fdividef(1.f, l_run);
+        const int col = hg * 128 + w * D + oc;
         const bf16* grow_ = p.qkvg + (long long)b * p.batch_stride + (long long)qi * p.seq_stride + p.g_col0 + col;
         bf16* orow = p.out + (long long)b * p.out_batch_stride + (long long)qi * p.out_seq_stride + col;
 #pragma unroll
-        for (int g8 = 0; g8 < D / 8; ++g8) {
+        for (int g8 = 0; g8 < 4; ++g8) {
           const uint4 gu = *reinterpret_cast<const uint4*>(grow_ + g8 * 8);
           const uint32_t gw[4] = {gu.x, gu.y, gu.z, gu.w};
           uint32_t ow[4];
@@ -533,6 +548,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           }
           *reinterpret_cast<uint4*>(orow + g8 * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
+      }
       }
     }
   }
@@ -611,11 +627,27 @@ int launch_bias_transpose(Ctx* c, const float* in, bf16* out, int H, int S, int 
 
 // qkvg: projection buffer ([B][S][width], or [S][B][width] when transposed); biasT: 16-bit [heads][query][ldq] holding FP16
 // values; mext: tiles from launch_mext ([B][KB][2048] or one row shared by all batch rows when mext_rows == 1).
+template <int D>
+static int launch_attn3(Ctx* c, int grid, const CUtensorMap& tmq, const CUtensorMap& tmkv, const CUtensorMap& tmb,
+                        const Attn3Args& a, cudaStream_t st) {
+  static bool attr_done[8] = {false};
+  if (!attr_done[c->device & 7]) {
+    cudaError_t e = cudaFuncSetAttribute(attn3_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, A3_SMEM);
+    if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "attention smem attribute: %s", cudaGetErrorString(e));
+    attr_done[c->device & 7] = true;
+  }
+  ProfScope ps(c, c->attn_tag, st);
+  attn3_kernel<D><<<grid, (A3_CTRL + 4 * (128 / D)) * 32, A3_SMEM, st>>>(tmq, tmkv, tmb, a);
+  return check_launch(c, "attn3_kernel");
+}
+
 int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0, int k_col0,
                       int v_col0, int g_col0, int heads, const bf16* biasT, int ldq, const bf16* mext, int mext_rows,
-                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st) {
-  if ((width & 7) || (ldq & 7) || (heads & 3) || ((q_col0 | k_col0 | v_col0 | g_col0) & 7))
-    return fail(c, XFOLD_ERR_ARG, "attention: width, column offsets and bias pitch must be multiples of 8, heads a multiple of 4");
+                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st, int head_dim) {
+  if (head_dim != 32 && head_dim != 64) return fail(c, XFOLD_ERR_ARG, "attention: head dimension must be 32 or 64");
+  const int per_item = 128 / head_dim;
+  if ((width & 7) || (ldq & 7) || (heads % per_item) || ((q_col0 | k_col0 | v_col0 | g_col0) & 7))
+    return fail(c, XFOLD_ERR_ARG, "attention: width, column offsets and bias pitch must be multiples of 8, heads x head dimension a multiple of 128");
   if (S <= 0 || B <= 0) return XFOLD_OK;
   CUtensorMap tmq, tmkv, tmb;
   bool ok;
@@ -650,18 +682,10 @@ int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int tra
   a.out_batch_stride = out_batch_stride;
   a.status = c->d_status;
   a.heads = heads;
-  static bool attr_done[8] = {false};
-  if (!attr_done[c->device & 7]) {
-    cudaError_t e = cudaFuncSetAttribute(attn3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A3_SMEM);
-    if (e != cudaSuccess) return fail(c, XFOLD_ERR_LAUNCH, "attention smem attribute: %s", cudaGetErrorString(e));
-    attr_done[c->device & 7] = true;
-  }
-  const long long items = (long long)((S + 127) / 128) * (heads / 4) * B;
+  const long long items = (long long)((S + 127) / 128) * (heads / per_item) * B;
   if (items * ((S + 63) / 64) >= (1ll << 30)) return fail(c, XFOLD_ERR_ARG, "attention: batch x heads x sequence too large for one launch");
   const int grid = (int)(items < c->sm_count ? items : c->sm_count);
-  ProfScope ps(c, c->attn_tag, st);
-  attn3_kernel<<<grid, A3_THREADS, A3_SMEM, st>>>(tmq, tmkv, tmb, a);
-  return check_launch(c, "attn3_kernel");
+  return head_dim == 32 ? launch_attn3<32>(c, grid, tmq, tmkv, tmb, a, st) : launch_attn3<64>(c, grid, tmq, tmkv, tmb, a, st);
 }
 
 }  // namespace xf

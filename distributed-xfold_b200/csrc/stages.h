@@ -43,16 +43,10 @@ int launch_mext(Ctx* c, const float* mask, long long mask_ld, bf16* out, int B, 
 int launch_bias_transpose(Ctx* c, const float* in, bf16* out, int H, int S, int ldq, cudaStream_t st);
 int launch_attention2(Ctx* c, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0, int k_col0,
                       int v_col0, int g_col0, int heads, const bf16* biasT, int ldq, const bf16* mext, int mext_rows,
-                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st);
+                      bf16* out, long long out_seq_stride, long long out_batch_stride, cudaStream_t st, int head_dim = 32);
 int launch_cm_ln(Ctx* c, const bf16* in, long long chan_stride, long long row_stride, int R, int N, bf16* out,
                  const float* gamma, const float* beta, float eps, cudaStream_t st);
 int launch_swiglu(Ctx* c, const bf16* in, bf16* out, long long rows, int F, cudaStream_t st);
-int launch_maskb(Ctx* c, const float* mask, long long mask_ld, float* out, int B, int S, int ld, cudaStream_t st);
-int launch_attention_op(Ctx* c, int D, const bf16* qkvg, int width, int S, int B, int transposed, int q_col0,
-                        int k_col0, int v_col0, int g_col0, int head_groups, const float* bias,
-                        long long bias_head_stride, int bias_ld, const float* maskb, int maskb_ld, bf16* out,
-                        long long out_seq_stride, long long out_batch_stride, cudaStream_t st);
-
 // ---- stages of the operators (api.cu); (chan, row) strides are in elements -------------------------------
 int trimul_project(Ctx* c, const bf16* z, const float* mask, int R, int N, int transposed_store,
                    const xfold_trimul_weights* w, bf16* x, bf16* a_out, bf16* b_out, bf16* g, long long chan_stride,

@@ -318,12 +318,27 @@ def transition_(x: torch.Tensor, w: PackedTransition):
     return x
 
 
+def prepare_pair_bias(pair_bias: torch.Tensor) -> torch.Tensor:
+    """float32 [H, S, S] -> the operand the attention kernel reads: float16 [H, S, pad8(S)] holding bias * log2(e)
+    (``xfold_pair_bias_prepare_fwd``).  Worth doing once when the same bias serves many calls (the diffusion
+    transformer's pair logits, the same for every denoising step)."""
+    _need_cuda(pair_bias)
+    assert pair_bias.dtype == torch.float32 and pair_bias.is_contiguous() and pair_bias.dim() == 3
+    h, s, s2 = pair_bias.shape
+    assert s == s2
+    dev = _dev(pair_bias)
+    out = torch.empty(h, s, (s + 7) // 8 * 8, dtype=torch.float16, device=pair_bias.device)
+    check(load().xfold_pair_bias_prepare_fwd(ctx(dev), _ptr(pair_bias), h, s, _ptr(out), _stream(dev)), dev,
+          "xfold_pair_bias_prepare_fwd")
+    return out
+
+
 def attention_pair_bias_core(xn: torch.Tensor, w: PackedSelfAttention, pair_bias: torch.Tensor,
                              mask: Optional[torch.Tensor]) -> torch.Tensor:
-    """xn bf16 [B, S, C] (normalised input), pair_bias float32 [H, S, S], mask float32 [S]
-    -> gated attention output bf16 [B, S, H * Dp] (head dim padded to Dp)."""
+    """xn bf16 [B, S, C] (normalised input), pair_bias float32 [H, S, S] or the float16 [H, S, pad8(S)] tensor of
+    ``prepare_pair_bias``, mask float32 [S] -> gated attention output bf16 [B, S, H * Dp] (head dim padded to Dp)."""
     _need_cuda(xn, pair_bias, mask)
-    assert xn.dtype == BF16 and xn.is_contiguous() and pair_bias.dtype == torch.float32 and pair_bias.is_contiguous()
+    assert xn.dtype == BF16 and xn.is_contiguous() and pair_bias.is_contiguous()
     dev = _dev(xn)
     b, s, cdim = xn.shape
     lib = load()
@@ -331,10 +346,15 @@ def attention_pair_bias_core(xn: torch.Tensor, w: PackedSelfAttention, pair_bias
     out = torch.empty(b, s, w.H * w.Dp, dtype=BF16, device=xn.device)
     if mask is not None:
         mask = mask.to(torch.float32).contiguous()
-    rc = lib.xfold_attention_pair_bias_core_fwd(ctx(dev), _ptr(xn), b, s, cdim, w.H, w.Dp, _ptr(w.w_qkvg), _ptr(w.bias),
-                                                _ptr(w.scale), _ptr(pair_bias), _ptr(mask), _ptr(out), _ptr(ws),
-                                                ws.numel(), _stream(dev))
-    check(rc, dev, "xfold_attention_pair_bias_core_fwd")
+    if pair_bias.dtype == torch.float16:
+        assert tuple(pair_bias.shape) == (w.H, s, (s + 7) // 8 * 8)
+        fn, name = lib.xfold_attention_pair_bias_core_prepared_fwd, "xfold_attention_pair_bias_core_prepared_fwd"
+    else:
+        assert pair_bias.dtype == torch.float32 and tuple(pair_bias.shape) == (w.H, s, s)
+        fn, name = lib.xfold_attention_pair_bias_core_fwd, "xfold_attention_pair_bias_core_fwd"
+    rc = fn(ctx(dev), _ptr(xn), b, s, cdim, w.H, w.Dp, _ptr(w.w_qkvg), _ptr(w.bias), _ptr(w.scale), _ptr(pair_bias),
+            _ptr(mask), _ptr(out), _ptr(ws), ws.numel(), _stream(dev))
+    check(rc, dev, name)
     return out
 
 

@@ -170,9 +170,19 @@ int xfold_attention_pair_bias_core_fwd(xfold_ctx* ctx, const void* xn, int B, in
                                        const float* pair_bias, const float* mask, void* out, void* ws,
                                        size_t ws_bytes, void* stream);
 
+/* The pair bias as the attention kernel reads it: 16-bit [H][S][pad8(S)], FP16 values times log2(e) (the kernel works in
+ * base 2).  A caller whose bias does not change between calls -- the diffusion transformer's pair logits are the same for
+ * all 200 denoising steps (nn/d_diffusion_transformer.py:296-305 recomputes them per call) -- converts it once with
+ * xfold_pair_bias_prepare_fwd (prepared: H * S * pad8(S) * 2 bytes) and passes it to the _prepared_ form of the core. */
+int xfold_pair_bias_prepare_fwd(xfold_ctx* ctx, const float* pair_bias, int H, int S, void* prepared, void* stream);
+int xfold_attention_pair_bias_core_prepared_fwd(xfold_ctx* ctx, const void* xn, int B, int S, int C, int H, int Dp,
+                                                const void* w_qkvg, const float* qkvg_bias, const float* qkvg_scale,
+                                                const void* prepared_bias, const float* mask, void* out, void* ws,
+                                                size_t ws_bytes, void* stream);
+
 /* The same core with one mask row per batch entry (mask float32, row b at mask + b * mask_ld; mask_ld = 0: one row for
  * all), which is what `_alpha_attention::grid_self_attn_forward` takes as its `bias` [B, 1, 1, S]
- * (csrc/Alpha_Attention.cpp:50-70); per-entry masks need Dp = 32. */
+ * (csrc/Alpha_Attention.cpp:50-70). */
 int xfold_gated_attention_core_fwd(xfold_ctx* ctx, const void* xn, int B, int S, int C, int H, int Dp, const void* w_qkvg,
                                    const float* qkvg_bias, const float* qkvg_scale, const float* pair_bias,
                                    const float* mask, long long mask_ld, void* out, void* ws, size_t ws_bytes,

@@ -14,7 +14,9 @@ def relf(a, b):
     return float((a - b).norm() / b.norm().clamp_min(1e-30))
 
 
-@pytest.mark.parametrize("n,samples,blocks", [(96, 1, 4), (150, 2, 8)])
+# the last case is the full depth of the reference's transformer (24 blocks in 6 super-blocks of 4,
+# nn/d_diffusion_transformer.py:267-310) at a size the CPU oracle finishes in seconds
+@pytest.mark.parametrize("n,samples,blocks", [(96, 1, 4), (150, 2, 8), (128, 1, 24)])
 def test_diffusion_transformer(ops, oracle, n, samples, blocks):
     from distributed_xfold_b200 import diffusion
     g = torch.Generator().manual_seed(1000 + n)

@@ -105,7 +105,7 @@ def test_transition(ops, oracle, rows, C):
     check_update(x, xd, ref)
 
 
-@pytest.mark.parametrize("B,S,C,H", [(1, 100, 384, 16), (2, 300, 768, 16), (1, 128, 384, 16)])
+@pytest.mark.parametrize("B,S,C,H", [(1, 100, 384, 16), (2, 300, 768, 16), (1, 128, 384, 16), (1, 520, 768, 16)])
 def test_attention_pair_bias_core(ops, oracle, B, S, C, H):
     g = torch.Generator().manual_seed(500 + S)
     st = oracle.make_self_attention_state(g, "", C, 0, False)
@@ -122,6 +122,10 @@ def test_attention_pair_bias_core(ops, oracle, B, S, C, H):
     w = ops.PackedSelfAttention(st, "", "cuda", H)
     out = ops.attention_pair_bias_core(xn.cuda().contiguous(), w, pb.cuda().contiguous(), mask.cuda())
     ops.synchronize_and_check()
+    # the same call with the bias converted once beforehand gives the same bits
+    out2 = ops.attention_pair_bias_core(xn.cuda().contiguous(), w, ops.prepare_pair_bias(pb.cuda().contiguous()), mask.cuda())
+    ops.synchronize_and_check()
+    assert torch.equal(out, out2)
     out = out.float().cpu().reshape(B, S, H, w.Dp)
     assert float(out[..., d:].abs().max()) == 0.0  # head padding stays zero
     assert relf(out[..., :d], ref) < 2e-2
