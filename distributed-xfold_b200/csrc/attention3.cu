@@ -103,6 +103,30 @@ __device__ __forceinline__ void tmem_st32_(uint32_t taddr, const uint32_t (&r)[3
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// Bounded wait for the control warps (producer, issuers), whose waits are long: between two looks at the barrier the
+// warp sleeps.  A warp that polls takes issue slots from the softmax warps of its scheduler (five polling warps were
+// measured at a quarter of the SM's issue slots, in a kernel that is bound by instruction issue); the price is up to
+// one sleep period of reaction time, which every event these warps wait for can afford.
+#ifndef A3_POLL_NS
+#define A3_POLL_NS 0u  // 0: the plain polling wait
+#endif
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int code) {
+  if (A3_POLL_NS == 0u) return mbar_wait(bar, parity, ab, code);
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 1;; ++spin) {
+    __nanosleep(A3_POLL_NS);
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0) {
+      if (*ab.cta_abort) return false;
+      if (clock64() - t0 > XF_WAIT_CYCLES) {
+        *ab.cta_abort = 1;
+        atomicCAS(ab.status, 0, code);
+        return false;
+      }
+    }
+  }
+}
 // true in exactly one lane of a converged warp
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -220,7 +244,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       for (uint32_t it = 0; it < my_items && okay; ++it) {
         int qt, hg, b;
         decode(it, qt, hg, b);
-        if (!mbar_wait(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
+        if (!mbar_wait_sleep(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
         mbar_arrive_expect_tx(q_full, A3_Q);
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -231,7 +255,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         const bf16* mrow = p.mext + (long long)b * p.mext_batch_stride;
         for (int kb = 0; kb < KB; ++kb, ++j) {
           const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
-          if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          if (!mbar_wait_sleep(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&k_full[st], A3_KV + 2048);
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -240,7 +264,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             else tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, kb * 64, b);
           }
           bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
-          if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          if (!mbar_wait_sleep(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&v_full[st], A3_KV);
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -279,8 +303,8 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       int akb = 0;
       auto issue_s = [&]() -> bool {
         const uint32_t ks = aj & 1u;
-        if (akb == 0 && !mbar_wait(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
-        if (!mbar_wait(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+        if (akb == 0 && !mbar_wait_sleep(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+        if (!mbar_wait_sleep(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
         tc_fence_after();
         if (leader) {
           const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
@@ -329,14 +353,14 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       for (uint32_t g = 0; g < G && okay; ++g) {
         const uint32_t par = g & 1u, vs = g & 1u, vpar = (g >> 1) & 1u;
         // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1
-        if (!mbar_wait(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!mbar_wait_sleep(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (g + 1 < G && !issue_s()) break;
         // the bias tile of the block's first half has been used up
-        if (!mbar_wait(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!mbar_wait_sleep(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (bi < n_half) issue_bias();
         const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
-        if (!mbar_wait(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
-        if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
+        if (!mbar_wait_sleep(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!v_ready && !mbar_wait_sleep(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
         tc_fence_after();
         if (leader) {
           const uint64_t vd = vd0 + uint64_t(vs * (A3_KV >> 4));
@@ -376,6 +400,9 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       decode(it, qt, hg, b);
       const int qi = qt * 128 + row;
       const bool qvalid = qi < p.S;
+#ifdef A3_STAGGER_EACH_ITEM
+      if (it > 0 && w > 0) __nanosleep(uint32_t(w) * A3_STAGGER_EACH_ITEM);
+#endif
       // m_ref: exponent offset in use (log2 units); it follows the running maximum lazily (see the file header).
       float m_ref = -3.0e38f, l_run = 0.f;
       bool next_ready = false;  // probe of this block's barrier, made before the previous block's second sweep
