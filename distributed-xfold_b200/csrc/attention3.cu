@@ -1,33 +1,35 @@
-// Gated attention for head dim 32 (TriangleAttention, 4 heads; AttentionPairBias with its 24-wide heads padded to
-// 32, 16 heads): the softmax warps never touch global memory, and sixteen of them are resident per SM.
+// Gated multi-head attention with an additive pair bias and a key mask (TriangleAttention: 4 heads x 32;
+// AttentionPairBias: 16 heads x 24 padded to 32 in the trunk, 16 x 48 padded to 64 in the diffusion transformer).
+// The softmax warps never touch global memory.
 //
-// Work item = 128 queries of one batch row x 4 heads; CTAs are persistent (one per SM) and run their items' 64-key
-// blocks as one continuous sequence.
-//   warp 0        : TMA producer.  Q per item (128 rows x 4 heads x 32 = two 64-column boxes); per 64-key block the K
-//                   tile (+ the 2 KB mask-bias tile) and the V tile, two stages each.
-//   warps 1..4    : tcgen05.mma issuers, one per head, so that no head ever waits for another.  Per block:
-//                       S  = Q K^T              (K = 32, N = 64)
-//                       S += E1 * Mext^T        (K = 16; column 0 of E1 is all ones, column 0 of Mext is the
-//                                                additive mask bias of each key)
-//                       O += P V                (K = 64, N = 32; P read from tensor memory, O stays there for the item)
-//                   Each issuer also fetches its head's pair-bias tiles (32-key halves, a ring of three).
-//   warps 5..20   : four softmax warpgroups, one per head, one thread per query row.
+// Work item = 128 queries of one batch row x 128 projection columns: four heads of 32 (D = 32, 24 warps) or two heads of
+// 64 (D = 64, 16 warps); CTAs are persistent (one per SM) and run their items' 64-key blocks as one continuous sequence.
+//   warp 0          : TMA producer.  Q per item (two 64-column boxes); per 64-key block the K tile (+ the 2 KB mask-bias
+//                     tile) and the V tile, two stages each.
+//   warps 1..NH     : tcgen05.mma issuers, one per head, so that no head ever waits for another; warp-uniform code, one
+//                     elected lane.  Per block:
+//                         S  = Q K^T              (K = D, N = 64)
+//                         S += E1 * Mext^T        (K = 16; column 0 of E1 is all ones, column 0 of Mext is the
+//                                                  additive mask bias of each key)
+//                         O += P V                (K = 64, N = D; P read from tensor memory, O stays there for the item)
+//                     Each issuer also fetches its head's pair-bias tiles (32-key halves, a ring of three).
+//   warps 8..8+4NH-1: one softmax warpgroup per head, one thread per query row.
 //
-// Why this shape.  The exponential unit (16 results per clock and SM) bounds the kernel: 4 x 128 x 64 exponentials
-// per block are 2048 clocks of it.  A softmax warp spends much of a block waiting (tensor-memory loads and stores,
-// barrier round trips, the dependent chain into the exponential); with two such warps per scheduler the unit idled
-// half of the time.  Four warps per scheduler need a thread to fit in ~96 registers, so a thread holds HALF a block
-// (32 logits) at a time: load 32 logits, sweep, store 16 packed probabilities, load the other 32 (after which the
-// logits buffer is free and the issuer already computes the next block's), sweep, store, publish.  Tensor memory is
-// then exactly full with single buffers: 4 x 64 columns of logits, 4 x 32 of output, 4 x 32 of probabilities.
+// Why this shape.  The exponential unit (16 results per clock and SM) sets the floor: 4 x 128 x 64 exponentials per block
+// are 2048 clocks of it.  Four warps per scheduler need a thread to fit in ~100 registers (setmaxnreg moves registers from
+// the control warps to the softmax warps), so a thread loads the block's 64 logits, releases the logits buffer (the issuer
+// already computes the next block's), and sweeps them in two halves of 32: exponent, exponential, 16 packed probabilities
+// stored, then the other half, then P is published.  Tensor memory is exactly full with single buffers for D = 32:
+// 4 x 64 columns of logits, 4 x 32 of output, 4 x 32 of probabilities.
 //
 // The sweep exponentiates against the running reference exponent m_ref of the PREVIOUS halves,
-//     x = s * log2(e) - m_ref (fp32) -> fp16x2,  + bias' (fp16x2; bias' = bias * log2(e) as delivered),
-//     ex2.approx.f16x2, row sum (fp16x2 partial sums of 8 terms), P as fp16,
+//     x = s * log2(e) - m_ref + bias'   (fp32; bias' = bias * log2(e) as delivered, FP16, added with the mixed-precision add),
+//     ex2.approx (fp32), P packed to fp16 pairs, row sum as fp16x2 partial sums of 8 terms,
 // and only looks at the partial sums afterwards: if one of them exceeds 2^8 in some row of the warp (a P > 256, i.e.
-// x > 8, shows there; fp16 would overflow beyond 2^16), the warp takes the exact path -- fp32 row maximum of the half still held in registers, O (tensor memory),
-// the row sum and, in a block's second half, the stored first half of P rescaled, the sweep repeated.  The first half
-// of an item always takes the exact path.  With trained or random weights the repeat is rare afterwards.
+// x > 8, shows there; fp16 would overflow beyond 2^16), the warp takes the exact path -- fp32 row maximum of the half
+// still held in registers, O (tensor memory), the row sum and, in a block's second half, the stored first half of P
+// rescaled, the sweep repeated.  The first half of an item always takes the exact path.  With trained or random weights
+// the repeat is rare afterwards.
 //
 // The pair bias arrives as FP16 [head][query][key], multiplied by log2(e) (key contiguous, row pitch a multiple of
 // 8); TMA lays a [128 queries][32 keys] tile out with the 64-byte swizzle, so the per-row 16-byte reads of the
@@ -54,11 +56,7 @@ struct Attn3Args {
 };
 
 constexpr int A3_CTRL = 8;                       // two control warpgroups: TMA producer, four MMA issuers, three idle warps
-constexpr int A3_THREADS = (A3_CTRL + 16) * 32;  // + four softmax warpgroups
 constexpr int A3_REGS_CTRL = 32, A3_REGS_SOFTMAX = 104;  // registers per thread after the re-balancing at kernel start
-#ifndef A3_STAGGER
-#define A3_STAGGER 600  // cycles between the first blocks of consecutive heads' softmax warpgroups (0: none)
-#endif
 constexpr uint32_t A3_Q = 32768;                 // [2 boxes][128 rows][64 columns]
 constexpr uint32_t A3_KV = 16384;                // [2 boxes][64 rows][64 columns]
 constexpr uint32_t A3_BT = 8192;                 // bias tile [128 queries][32 keys] fp16
@@ -102,30 +100,6 @@ __device__ __forceinline__ void tmem_st32_(uint32_t taddr, const uint32_t (&r)[3
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
-}
-// Bounded wait for the control warps (producer, issuers), whose waits are long: between two looks at the barrier the
-// warp sleeps.  A warp that polls takes issue slots from the softmax warps of its scheduler (five polling warps were
-// measured at a quarter of the SM's issue slots, in a kernel that is bound by instruction issue); the price is up to
-// one sleep period of reaction time, which every event these warps wait for can afford.
-#ifndef A3_POLL_NS
-#define A3_POLL_NS 0u  // 0: the plain polling wait
-#endif
-__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, const AbortCtx& ab, int code) {
-  if (A3_POLL_NS == 0u) return mbar_wait(bar, parity, ab, code);
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t spin = 1;; ++spin) {
-    __nanosleep(A3_POLL_NS);
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((spin & 63u) == 0) {
-      if (*ab.cta_abort) return false;
-      if (clock64() - t0 > XF_WAIT_CYCLES) {
-        *ab.cta_abort = 1;
-        atomicCAS(ab.status, 0, code);
-        return false;
-      }
-    }
-  }
 }
 // true in exactly one lane of a converged warp
 __device__ __forceinline__ bool elect_one() {
@@ -244,7 +218,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       for (uint32_t it = 0; it < my_items && okay; ++it) {
         int qt, hg, b;
         decode(it, qt, hg, b);
-        if (!mbar_wait_sleep(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
+        if (!mbar_wait(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
         mbar_arrive_expect_tx(q_full, A3_Q);
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
@@ -255,7 +229,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         const bf16* mrow = p.mext + (long long)b * p.mext_batch_stride;
         for (int kb = 0; kb < KB; ++kb, ++j) {
           const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
-          if (!mbar_wait_sleep(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&k_full[st], A3_KV + 2048);
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -264,7 +238,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             else tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, kb * 64, b);
           }
           bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
-          if (!mbar_wait_sleep(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+          if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&v_full[st], A3_KV);
 #pragma unroll
           for (int x = 0; x < 2; ++x) {
@@ -303,8 +277,8 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       int akb = 0;
       auto issue_s = [&]() -> bool {
         const uint32_t ks = aj & 1u;
-        if (akb == 0 && !mbar_wait_sleep(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
-        if (!mbar_wait_sleep(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+        if (akb == 0 && !mbar_wait(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+        if (!mbar_wait(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
         tc_fence_after();
         if (leader) {
           const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
@@ -353,14 +327,14 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
       for (uint32_t g = 0; g < G && okay; ++g) {
         const uint32_t par = g & 1u, vs = g & 1u, vpar = (g >> 1) & 1u;
         // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1
-        if (!mbar_wait_sleep(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!mbar_wait(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (g + 1 < G && !issue_s()) break;
         // the bias tile of the block's first half has been used up
-        if (!mbar_wait_sleep(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!mbar_wait(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
         if (bi < n_half) issue_bias();
         const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
-        if (!mbar_wait_sleep(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
-        if (!v_ready && !mbar_wait_sleep(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
+        if (!mbar_wait(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+        if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
         tc_fence_after();
         if (leader) {
           const uint64_t vd = vd0 + uint64_t(vs * (A3_KV >> 4));
@@ -389,20 +363,11 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
     const uint32_t FULL = 0xffffffffu;
     uint32_t g = 0, bslot = 0;  // block number; bias ring position
     bool okay = true;
-    if (A3_STAGGER > 0 && w > 0) {
-      // the four heads share each scheduler's exponential unit: start them a fraction of a block apart, so that one
-      // head's loads, stores and barrier round trips fall into the others' sweeps
-      const long long t0 = clock64();
-      while (clock64() - t0 < (long long)w * A3_STAGGER) {}
-    }
     for (uint32_t it = 0; it < my_items && okay; ++it) {
       int qt, hg, b;
       decode(it, qt, hg, b);
       const int qi = qt * 128 + row;
       const bool qvalid = qi < p.S;
-#ifdef A3_STAGGER_EACH_ITEM
-      if (it > 0 && w > 0) __nanosleep(uint32_t(w) * A3_STAGGER_EACH_ITEM);
-#endif
       // m_ref: exponent offset in use (log2 units); it follows the running maximum lazily (see the file header).
       float m_ref = -3.0e38f, l_run = 0.f;
       bool next_ready = false;  // probe of this block's barrier, made before the previous block's second sweep
@@ -419,18 +384,25 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         uint32_t r[64];
         tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
         tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
-        // has the previous block's P V product read P?  (needed before this block's first P store)
-        bool pv_ok = (g == 0) || mbar_test_wait(&pv_done[w], (g - 1) & 1u);
+        // While the logits are on their way, the previous block's P (its second store was issued a moment ago) completes:
+        // it is published together with the release of the logits buffer, so that neither the completion of that store
+        // nor the latency of this load is waited for on its own.  (An item's last block publishes itself.)
+        if (kb > 0) tmem_st_wait_();
         tmem_ld_wait();
         // the whole block of logits is in registers: the issuer may overwrite the buffer with the next block's
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&s_free[w]);
+        if (lane == 0) {
+          mbar_arrive(&s_free[w]);
+          if (kb > 0) mbar_arrive(&p_ready[w]);
+        }
+        // has the previous block's P V product read P?  (needed before this block's first P store; it is issued about
+        // now, so it is probed during the first sweep; an item's first block follows an awaited product)
+        bool pv_ok = (kb == 0);
         next_ready = false;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const uint8_t* bt = my_bias + bslot * A3_BT;
-          if (h == 1) next_ready = (kb + 1 < KB) && mbar_test_wait(&my_sb[(g + 1) & 1u], ((g + 1) >> 1) & 1u);
           bool exact = (kb == 0 && h == 0);
           __half2 hs[4];
           uint32_t pk[16];
@@ -494,6 +466,13 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             for (int e = 0; e < 4; ++e) hs[e] = __float2half2_rn(0.f);
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
+              // probes whose answers are wanted right after this sweep: issued before its last quarter, so that the
+              // barrier's answer time passes behind arithmetic
+              if (c4 == 3) {
+                if (h == 0 && !pv_ok) pv_ok = mbar_test_wait(&pv_done[w], (g - 1) & 1u);
+                if (h == 1 && !next_ready && kb + 1 < KB)
+                  next_ready = mbar_test_wait(&my_sb[(g + 1) & 1u], ((g + 1) >> 1) & 1u);
+              }
               const uint4 bq = *reinterpret_cast<const uint4*>(bt + ((uint32_t(c4) ^ bsw) << 4));
               const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
@@ -526,7 +505,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           l_run += ls0 + ls1;
           if (h == 0) {
             // the P V product of the previous block must have read P before it is overwritten (probed at the block's start)
-            if (!__all_sync(FULL, pv_ok)) pv_ok = mbar_test_wait(&pv_done[w], (g - 1) & 1u);  // a second look, a sweep later
+            if (!__all_sync(FULL, pv_ok)) pv_ok = mbar_test_wait(&pv_done[w], (g - 1) & 1u);
             if (!__all_sync(FULL, pv_ok)) {
               okay = __all_sync(FULL, mbar_wait(&pv_done[w], (g - 1) & 1u, ab, XF_ERR_WAIT_ATTN));
               if (!okay) break;
@@ -536,15 +515,17 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             __syncwarp();
             if (lane == 0) mbar_arrive(&b_free[w]);  // this half's bias tile has been read by the whole warp
           } else {
-            tmem_st16_(p_addr + 16, pk);
-            tmem_st_wait_();
+            tmem_st16_(p_addr + 16, pk);  // completes behind the next block's load of the logits
           }
           if (++bslot == A3_BS) bslot = 0;
         }
         if (!okay) break;
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_ready[w]);
+        if (kb == KB - 1) {  // nothing of this item follows: publish now
+          tmem_st_wait_();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_ready[w]);
+        }
       }
       if (!okay || KB == 0) break;
       // item epilogue: O / l, gate, store
