@@ -163,12 +163,14 @@ def run_multi(args, world, rank, local_rank):
         roof = None
         if "trimul_contract" in per_kernel:
             sec = per_kernel["trimul_contract"]["avg_ms"] * 1e-3
-            ach = 2.0 * r * n * n * 128 / sec / 1e12
+            # a rank contracts 128 / world channels of N x N x N, in as many launches as the stage is chunked into
+            per_launch = 2.0 * nb * (2.0 * n ** 3 * 128 / world) / per_kernel["trimul_contract"]["launches_per_step"]
+            ach = per_launch / sec / 1e12
             roof = {"kernel": "trimul_contract", "bound": "tensor", "achieved": ach, "peak": tf_sust, "unit": "TFLOP/s",
                     "frac": ach / tf_sust, "traffic": None, "peak_source": which + " (sustained)",
                     "share_of_step": per_kernel["trimul_contract"]["ms_per_step"] / ms_prof,
-                    "note": "per-rank kernel (this rank's share of the contraction); no ncu capture is taken of a "
-                            "multi-rank run, so traffic is not reported here"}
+                    "note": "per-rank launches (this rank's channels, one chunk of them per launch); no ncu capture is "
+                            "taken of a multi-rank run, so traffic is not reported here"}
         xbytes = exchange_bytes_per_block(sh) * nb
         xms = per_kernel.get("peer_exchange", {}).get("ms_per_step")
         exchange = {"bytes_sent_per_rank_per_step": xbytes, "nvlink_floor_ms": xbytes / (NVLINK_GBS * 1e9) * 1e3,
