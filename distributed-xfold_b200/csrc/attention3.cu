@@ -4,8 +4,9 @@
 //
 // Work item = 128 queries of one batch row x 128 projection columns: four heads of 32 (D = 32, 24 warps) or two heads of
 // 64 (D = 64, 16 warps); CTAs are persistent (one per SM) and run their items' 64-key blocks as one continuous sequence.
-//   warp 0          : TMA producer.  Q per item (two 64-column boxes); per 64-key block the K tile (+ the 2 KB mask-bias
-//                     tile) and the V tile, two stages each.
+//   warps 0 and 7   : TMA producers.  Warp 0: Q per item (two 64-column boxes) and per 64-key block the K tile (+ the 2 KB
+//                     mask-bias tile); warp 7: the V tile per block; two stages each.  (One lane doing all of it was
+//                     measured as a pacemaker of the kernel.)
 //   warps 1..NH     : tcgen05.mma issuers, one per head, so that no head ever waits for another; warp-uniform code, one
 //                     elected lane.  Per block:
 //                         S  = Q K^T              (K = D, N = 64)
@@ -205,11 +206,8 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
   // Register re-balancing (whole warpgroups): the control warps run single threads with a handful of values, the
   // softmax threads hold a block's 64 logits and 16 packed probabilities.
   // (With two heads per item the CTA has 512 threads and every thread 128 registers from the start.)
-  if constexpr (NH == 4) {
-    if (warp < A3_CTRL) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
-    else asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A3_REGS_SOFTMAX));
-  }
-
+  if (warp < A3_CTRL) {
+  if constexpr (NH == 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
   if (warp == 0) {
     // ------------------------------------------------------------------------------------------- TMA producer
     if (lane == 0) {
@@ -238,6 +236,19 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             else tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, kb * 64, b);
           }
           bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
+        }
+      }
+    }
+  } else if (warp == 7) {
+    // ------------------------------------------------------------------------------------------- TMA producer of V
+    if (lane == 0) {
+      uint32_t j = 0;
+      bool okay = true;
+      for (uint32_t it = 0; it < my_items && okay; ++it) {
+        int qt, hg, b;
+        decode(it, qt, hg, b);
+        for (int kb = 0; kb < KB; ++kb, ++j) {
+          const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
           if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
           mbar_arrive_expect_tx(&v_full[st], A3_KV);
 #pragma unroll
@@ -348,7 +359,9 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
         if (++kb == KB) kb = 0;
       }
     }
-  } else if (warp >= A3_CTRL) {
+  }
+  } else {
+    if constexpr (NH == 4) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A3_REGS_SOFTMAX));
     // ------------------------------------------------------------------------------------------- softmax warps
     const int w = (warp - A3_CTRL) >> 2;
     const int q4 = warp & 3;  // TMEM lane quarter this warp may access
