@@ -111,6 +111,7 @@ SIGNATURES = {
     "xfold_shard_ctx_create": (ci, [vp, C.POINTER(ShardDesc), C.POINTER(vp)]),
     "xfold_shard_ctx_destroy": (None, [vp]),
     "xfold_shard_workspace_bytes": (sz, [vp]),
+    "xfold_shard_ctx_set_overlap": (ci, [vp, ci, ci]),
     "xfold_pairformer_stack_sharded_fwd": (ci, [vp, vp, ci, vp, vp, vp, C.POINTER(PairformerWeights), ci, vp, sz, vp,
                                                 C.POINTER(ci)]),
     "xfold_trimul_contract_planes_incoming_fwd": (ci, [vp, vp, vp, ci, ci, ci, ci, ci, vp, ci, vp]),

@@ -122,19 +122,30 @@ static int linear_gate_resid(Ctx* c, const bf16* x, long long ldx, long long M, 
 static int linear_gate_resid_chunked(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* w, int N,
                                      const bf16* resid, long long ldr, bf16* out, long long ldo, cudaStream_t st,
                                      const ChunkHook* hook) {
-  if (!hook || hook->parts <= 1 || !hook->after)
+  if (!hook || !hook->after)
     return linear_gate_resid(c, x, ldx, M, K, w, N, nullptr, 0, 0, resid, ldr, out, ldo, st);
+  if (hook->parts <= 1) {  // one chunk: the hook still runs, after the whole projection
+    const int rc = linear_gate_resid(c, x, ldx, M, K, w, N, nullptr, 0, 0, resid, ldr, out, ldo, st);
+    return rc ? rc : hook->after(0, M);
+  }
   const long long unit = hook->unit > 0 ? hook->unit : 1;
   long long per = (M + hook->parts - 1) / hook->parts;
   per = (per + unit - 1) / unit * unit;
-  for (long long m0 = 0; m0 < M; m0 += per) {
-    const long long m = M - m0 < per ? M - m0 : per;
-    int rc = linear_gate_resid(c, x + m0 * ldx, ldx, m, K, w, N, nullptr, 0, 0, resid ? resid + m0 * ldr : nullptr, ldr,
-                               out + m0 * ldo, ldo, st);
-    if (rc) return rc;
-    if ((rc = hook->after(m0, m))) return rc;
+  const int sms0 = c->gemm_sms, cap0 = c->peer_cta_cap;
+  if (hook->reserve_sms > 0 && hook->reserve_sms < c->sm_count) {
+    c->gemm_sms = c->sm_count - hook->reserve_sms;
+    c->peer_cta_cap = hook->reserve_sms * 8;
   }
-  return XFOLD_OK;
+  int rc = XFOLD_OK;
+  for (long long m0 = 0; m0 < M && !rc; m0 += per) {
+    const long long m = M - m0 < per ? M - m0 : per;
+    rc = linear_gate_resid(c, x + m0 * ldx, ldx, m, K, w, N, nullptr, 0, 0, resid ? resid + m0 * ldr : nullptr, ldr,
+                           out + m0 * ldo, ldo, st);
+    if (!rc) rc = hook->after(m0, m);
+  }
+  c->gemm_sms = sms0;
+  c->peer_cta_cap = cap0;
+  return rc;
 }
 
 static int linear_swiglu(Ctx* c, const bf16* x, long long ldx, long long M, int K, const bf16* wp, int F, bf16* out,

@@ -459,7 +459,8 @@ static int launch_one(Ctx* c, const CUtensorMap& tmA, const CUtensorMap& tmB, co
         return fail(c, XFOLD_ERR_ARG, "gemm: cannot encode the gate tensor map");
     }
   }
-  const int grid = (int)(total < c->sm_count ? total : c->sm_count);
+  const int sms = c->gemm_sms > 0 && c->gemm_sms < c->sm_count ? c->gemm_sms : c->sm_count;
+  const int grid = (int)(total < sms ? total : sms);
   const int tag = EPI == EPI_TRIMUL_AB ? XFOLD_K_TRIMUL_PROJ
                   : EPI == EPI_SWIGLU  ? XFOLD_K_LINEAR_SWIGLU
                   : EPI == EPI_GATE_RESID ? XFOLD_K_LINEAR_GATE_RESID

@@ -26,6 +26,10 @@ struct Ctx {
   long long launch_count = 0;  // kernels launched through this context
   int prof_on = 0;             // when set, every launch is bracketed by a pair of CUDA events
   int attn_tag = XFOLD_K_ATTENTION;  // kernel class the attention launchers account their launch to
+  // While a stage's exchange kernels are meant to run beside its GEMMs (second stream), the persistent GEMMs leave some
+  // SMs free and the exchange kernels are sized for them: a GEMM CTA fills its SM, so without free SMs the two serialise.
+  int gemm_sms = 0;      // SMs a GEMM launch may take (0: all)
+  int peer_cta_cap = 0;  // CTAs of a peer exchange kernel (0: its own default)
   std::vector<ProfRec> prof_recs, prof_pool;
 };
 

@@ -189,7 +189,7 @@ int launch_transpose_scatter(Ctx* c, const bf16* z, int R, int N, int row0, void
   const PeerTable pt = make_table(dst, col_starts, world, N);
   const long long total = (long long)R * N * 16;
   long long blocks = (total + 255) / 256;
-  const long long cap = (long long)c->sm_count * 16;
+  const long long cap = c->peer_cta_cap > 0 ? c->peer_cta_cap : (long long)c->sm_count * 16;
   if (blocks > cap) blocks = cap;
   ProfScope ps(c, XFOLD_K_PEER, st);
   transpose_scatter_kernel<<<(int)blocks, 256, 0, st>>>(z, R, N, row0, pt);
@@ -202,7 +202,7 @@ int launch_channel_scatter(Ctx* c, const bf16* a, const bf16* b, int R, int N, i
   const PeerTable pa = make_table(peer_a, nullptr, world, 0), pb = make_table(peer_b, nullptr, world, 0);
   const long long rows = (long long)R * 128 * 2;
   long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)c->sm_count * 8;
+  const long long cap = c->peer_cta_cap > 0 ? c->peer_cta_cap : (long long)c->sm_count * 8;
   if (blocks > cap) blocks = cap;
   ProfScope ps(c, XFOLD_K_PEER, st);
   channel_scatter_kernel<<<(int)blocks, 256, 0, st>>>(a, b, R, N, ld, row0, 128 / world, pa, pb);
@@ -215,7 +215,7 @@ int launch_row_scatter(Ctx* c, const bf16* o, int channels, int chan0, int N, in
   const PeerTable pt = make_table(peer_o, row_starts, world, N);
   const long long rows = (long long)channels * N;
   long long blocks = (rows + 7) / 8;
-  const long long cap = (long long)c->sm_count * 8;
+  const long long cap = c->peer_cta_cap > 0 ? c->peer_cta_cap : (long long)c->sm_count * 8;
   if (blocks > cap) blocks = cap;
   ProfScope ps(c, XFOLD_K_PEER, st);
   row_scatter_kernel<<<(int)blocks, 256, 0, st>>>(o, channels, N, ldo, chan0, pt);

@@ -41,7 +41,24 @@ struct ShardCtx {
   cudaStream_t side = nullptr;
   cudaEvent_t ev[8] = {nullptr};
   int ev_next = 0;
-  int parts = 2;  // chunks per producing stage
+  int parts = 2;    // chunks per producing stage
+  int reserve = 0;  // SMs the chunked GEMMs leave free for the exchange kernels on the second stream
+};
+
+// For the lifetime of the object the context's GEMMs leave `reserve` SMs free and its exchange kernels are sized for them.
+struct OverlapScope {
+  Ctx* c;
+  int sms0, cap0;
+  OverlapScope(Ctx* c_, const ShardCtx* sc, bool chunked) : c(c_), sms0(c_->gemm_sms), cap0(c_->peer_cta_cap) {
+    if (chunked && sc->reserve > 0 && sc->reserve < c->sm_count) {
+      c->gemm_sms = c->sm_count - sc->reserve;
+      c->peer_cta_cap = sc->reserve * 8;
+    }
+  }
+  ~OverlapScope() {
+    c->gemm_sms = sms0;
+    c->peer_cta_cap = cap0;
+  }
 };
 
 // side stream waits for what `main` has launched so far
@@ -104,11 +121,14 @@ static int barrier(Ctx* c, ShardCtx* sc, cudaStream_t st) {
 static int trimul_sharded(Ctx* c, ShardCtx* sc, bf16* z, const float* mask_rows, const xfold_trimul_weights* w, int outgoing,
                           const ShardWs& W, cudaStream_t st) {
   const int me = sc->rank, N = sc->n, ld = sc->ld, R = sc->start[me + 1] - sc->start[me], row0 = sc->start[me];
-  int rc;
   // a, b for this rank's rows, all channels: [R][128][ld]; the rows of a finished chunk leave for their planes on the
   // second stream while the next chunk is projected
   const int parts = sc->parts > 1 && R >= 2 * sc->parts ? sc->parts : 1;
   const int rper = (R + parts - 1) / parts;
+  const int cparts = sc->parts > 1 && sc->cq >= 2 * sc->parts ? sc->parts : 1;
+  int rc;
+  {
+  OverlapScope ov(c, sc, parts > 1);
   for (int r0 = 0; r0 < R; r0 += rper) {
     const int rr = R - r0 < rper ? R - r0 : rper;
     const long long t0 = (long long)r0 * N;
@@ -119,6 +139,7 @@ static int trimul_sharded(Ctx* c, ShardCtx* sc, bf16* z, const float* mask_rows,
     if ((rc = launch_channel_scatter(c, W.a + (long long)r0 * 128 * ld, W.b + (long long)r0 * 128 * ld, rr, N, ld, row0 + r0,
                                      sc->pa, sc->pb, sc->world, sc->side))) return rc;
   }
+  }
   if ((rc = join_side(c, sc, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
   // this rank's channels, all rows: planes [cq][N][ld]
@@ -126,8 +147,9 @@ static int trimul_sharded(Ctx* c, ShardCtx* sc, bf16* z, const float* mask_rows,
   const bf16* pb = (const bf16*)sc->pb[me];
   const long long cs = (long long)N * ld;
   // the product in groups of channels; a finished group's rows go back to their owners while the next group is computed
-  const int cparts = sc->parts > 1 && sc->cq >= 2 * sc->parts ? sc->parts : 1;
   const int cper = (sc->cq + cparts - 1) / cparts;
+  {
+  OverlapScope ov(c, sc, cparts > 1);
   for (int c0 = 0; c0 < sc->cq; c0 += cper) {
     const int cc = sc->cq - c0 < cper ? sc->cq - c0 : cper;
     const long long off = (long long)c0 * cs;
@@ -136,6 +158,7 @@ static int trimul_sharded(Ctx* c, ShardCtx* sc, bf16* z, const float* mask_rows,
     if (rc) return rc;
     if ((rc = fork_to_side(c, sc, st))) return rc;
     if ((rc = launch_row_scatter(c, W.op + off, cc, me * sc->cq + c0, N, ld, sc->po, sc->start, sc->world, sc->side))) return rc;
+  }
   }
   if ((rc = join_side(c, sc, st))) return rc;
   if ((rc = barrier(c, sc, st))) return rc;
@@ -161,6 +184,7 @@ static int block_sharded(Ctx* c, ShardCtx* sc, int* slot, bf16* s, const float* 
   // shard (zT[j][i] = z[i][j], in the OTHER buffer of the rank that owns column j) on the second stream meanwhile.
   ChunkHook to_t;
   to_t.parts = sc->parts;
+  to_t.reserve_sms = sc->reserve;
   to_t.unit = N;
   bf16* src = z;
   int dst_slot = *slot ^ 1;
@@ -264,6 +288,13 @@ void xfold_shard_ctx_destroy(xfold_shard_ctx* sc) {
 }
 
 size_t xfold_shard_workspace_bytes(const xfold_shard_ctx* sc) { return sc ? carve_shard(nullptr, 0, *sc).bytes : 0; }
+
+int xfold_shard_ctx_set_overlap(xfold_shard_ctx* sc, int chunks, int reserved_sms) {
+  if (!sc || chunks < 1 || chunks > 8 || reserved_sms < 0 || reserved_sms > 64) return XFOLD_ERR_ARG;
+  sc->parts = chunks;
+  sc->reserve = reserved_sms;
+  return XFOLD_OK;
+}
 
 int xfold_pairformer_stack_sharded_fwd(xfold_ctx* cx, xfold_shard_ctx* sc, int z_slot, void* s, const float* pair_mask,
                                        const float* seq_mask, const xfold_pairformer_weights* blocks, int num_blocks,

@@ -30,6 +30,7 @@ struct Carver {
 // The multi-GPU block uses it to send finished rows to their next owner on a second stream while the rest computes.
 struct ChunkHook {
   int parts = 1;
+  int reserve_sms = 0;  // SMs the chunks' GEMMs leave free for what the hook launches on another stream
   long long unit = 1;
   std::function<int(long long, long long)> after;
 };

@@ -286,7 +286,7 @@ class ShardedTrunk:
     World sizes 2, 4 and 8 (the channel slices of the TriangleMultiplication need 128 % world == 0); for anything else,
     and on the CPU, ``pairformer_block`` above composes the same stages with collectives."""
 
-    def __init__(self, sh: "RowSharding", device):
+    def __init__(self, sh: "RowSharding", device, chunks: Optional[int] = None, reserved_sms: int = 0):
         import ctypes as C
         import torch.distributed._symmetric_memory as symm
         from . import _cabi
@@ -329,6 +329,9 @@ class ShardedTrunk:
         _cabi.check(lib.xfold_shard_ctx_create(_cabi.ctx(self.dev), C.byref(desc), C.byref(out)), self.dev,
                     "xfold_shard_ctx_create")
         self.handle = out.value
+        if chunks is not None:   # chunks of a producing stage whose rows travel while the next chunk is computed
+            _cabi.check(lib.xfold_shard_ctx_set_overlap(self.handle, int(chunks), int(reserved_sms)), self.dev,
+                        "xfold_shard_ctx_set_overlap")
         self.ws = torch.empty(lib.xfold_shard_workspace_bytes(self.handle), dtype=torch.uint8, device=self.device)
         self.slot = 0
 

@@ -123,6 +123,18 @@ def _trunk_rank_main(rank, world, port, n, pad, nblocks, ret):
         ret["z"], ret["s"] = full.float().cpu(), sd.float().cpu()
     dist.barrier()
     trunk.close()
+    # other overlap settings (one chunk: the exchanges follow their GEMMs; four chunks with SMs left free for the
+    # exchange kernels) change the schedule only: same bits
+    ref_rows, ref_s = zs.clone(), sd.clone()
+    for chunks, reserve in ((1, 0), (4, 12)):
+        other = row_sharded.ShardedTrunk(sh, f"cuda:{rank}", chunks=chunks, reserved_sms=reserve)
+        other.load(z[sh.rows].to(BF).cuda())
+        sd.copy_(s.to(BF).cuda())
+        zo = other.run(sd, pmd, smd, stack)
+        ops.synchronize_and_check(rank)
+        assert torch.equal(zo, ref_rows) and torch.equal(sd, ref_s), (chunks, reserve)
+        dist.barrier()
+        other.close()
     dist.destroy_process_group()
 
 
