@@ -41,7 +41,10 @@ struct ShardCtx {
   cudaStream_t side = nullptr;
   cudaEvent_t ev[8] = {nullptr};
   int ev_next = 0;
-  int parts = 2;    // chunks per producing stage
+  // Chunks per producing stage.  One: every exchange follows its GEMM.  More were measured as no faster on 2-8 GPUs (a
+  // persistent GEMM CTA fills its SM, so exchange kernels and GEMMs take turns) and, at N = 128 on two GPUs, gave
+  // results that changed from run to run; with one chunk the sharded path reproduces the one-GPU path bit for bit.
+  int parts = 1;
   int reserve = 0;  // SMs the chunked GEMMs leave free for the exchange kernels on the second stream
 };
 

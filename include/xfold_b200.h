@@ -345,10 +345,12 @@ typedef struct {
 int xfold_shard_ctx_create(xfold_ctx* ctx, const xfold_shard_desc* desc, xfold_shard_ctx** out);
 void xfold_shard_ctx_destroy(xfold_shard_ctx* sc);
 size_t xfold_shard_workspace_bytes(const xfold_shard_ctx* sc);
-/* Overlap of the exchanges with the GEMMs that produce their data: a producing stage is cut into `chunks` (1..8, default 2)
- * so that a finished chunk's rows travel to their owners on the context's second stream while the next chunk is computed;
- * the chunked GEMMs leave `reserved_sms` SMs (0..64, default 0) free, for which the exchange kernels are then sized -- a
- * persistent GEMM CTA fills its SM, so with none reserved the two kinds of kernel take turns instead of running together. */
+/* EXPERIMENTAL overlap of the exchanges with the GEMMs that produce their data: a producing stage is cut into `chunks`
+ * (1..8, default 1 = off) so that a finished chunk's rows travel to their owners on the context's second stream while the
+ * next chunk is computed; the chunked GEMMs leave `reserved_sms` SMs (0..64, default 0) free, for which the exchange
+ * kernels are then sized -- a persistent GEMM CTA fills its SM, so with none reserved the two kinds of kernel take turns.
+ * Measured as no faster on 2-8 GPUs, and with more than one chunk small problems (N = 128 on two GPUs) gave results that
+ * varied between runs; the default reproduces the one-GPU path bit for bit. */
 int xfold_shard_ctx_set_overlap(xfold_shard_ctx* sc, int chunks, int reserved_sms);
 int xfold_pairformer_stack_sharded_fwd(xfold_ctx* ctx, xfold_shard_ctx* sc, int z_slot, void* s, const float* pair_mask,
                                        const float* seq_mask, const xfold_pairformer_weights* blocks, int num_blocks,
