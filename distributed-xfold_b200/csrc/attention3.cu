@@ -207,159 +207,159 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
   // softmax threads hold a block's 64 logits and 16 packed probabilities.
   // (With two heads per item the CTA has 512 threads and every thread 128 registers from the start.)
   if (warp < A3_CTRL) {
-  if constexpr (NH == 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
-  if (warp == 0) {
-    // ------------------------------------------------------------------------------------------- TMA producer
-    if (lane == 0) {
-      uint32_t j = 0;  // block number
-      bool okay = true;
-      for (uint32_t it = 0; it < my_items && okay; ++it) {
-        int qt, hg, b;
-        decode(it, qt, hg, b);
-        if (!mbar_wait(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(q_full, A3_Q);
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const int col = p.q_col0 + hg * 128 + x * 64;
-          if (p.transposed) tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, b, qt * 128);
-          else tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, qt * 128, b);
-        }
-        const bf16* mrow = p.mext + (long long)b * p.mext_batch_stride;
-        for (int kb = 0; kb < KB; ++kb, ++j) {
-          const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
-          if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-          mbar_arrive_expect_tx(&k_full[st], A3_KV + 2048);
-#pragma unroll
+    if constexpr (NH == 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(A3_REGS_CTRL));
+    if (warp == 0) {
+      // ------------------------------------------------------------------------------------------- TMA producer
+      if (lane == 0) {
+        uint32_t j = 0;  // block number
+        bool okay = true;
+        for (uint32_t it = 0; it < my_items && okay; ++it) {
+          int qt, hg, b;
+          decode(it, qt, hg, b);
+          if (!mbar_wait(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
+          mbar_arrive_expect_tx(q_full, A3_Q);
+  #pragma unroll
           for (int x = 0; x < 2; ++x) {
-            const int col = p.k_col0 + hg * 128 + x * 64;
-            if (p.transposed) tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, b, kb * 64);
-            else tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, kb * 64, b);
+            const int col = p.q_col0 + hg * 128 + x * 64;
+            if (p.transposed) tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, b, qt * 128);
+            else tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, qt * 128, b);
           }
-          bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
-        }
-      }
-    }
-  } else if (warp == 7) {
-    // ------------------------------------------------------------------------------------------- TMA producer of V
-    if (lane == 0) {
-      uint32_t j = 0;
-      bool okay = true;
-      for (uint32_t it = 0; it < my_items && okay; ++it) {
-        int qt, hg, b;
-        decode(it, qt, hg, b);
-        for (int kb = 0; kb < KB; ++kb, ++j) {
-          const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
-          if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
-          mbar_arrive_expect_tx(&v_full[st], A3_KV);
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            const int col = p.v_col0 + hg * 128 + x * 64;
-            if (p.transposed) tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, b, kb * 64);
-            else tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, kb * 64, b);
+          const bf16* mrow = p.mext + (long long)b * p.mext_batch_stride;
+          for (int kb = 0; kb < KB; ++kb, ++j) {
+            const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
+            if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+            mbar_arrive_expect_tx(&k_full[st], A3_KV + 2048);
+  #pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              const int col = p.k_col0 + hg * 128 + x * 64;
+              if (p.transposed) tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, b, kb * 64);
+              else tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, kb * 64, b);
+            }
+            bulk_load(sMext + st * 2048, mrow + (long long)kb * 1024, 2048, &k_full[st]);
           }
         }
       }
-    }
-  } else if (warp <= NH) {
-    // ------------------------------------------------------------------------------------------- MMA issuer of head w
-    // The whole warp runs this code with identical values in every lane (waits included), and one elected lane issues
-    // the tensor-core and TMA instructions: descriptors and counters are warp-uniform, built once outside the loop.
-    {
-      const int w = warp - 1;
-      const bool leader = elect_one();
-      constexpr uint32_t idesc_s = make_idesc(128, 64);
-      constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
-                                                                  // projection buffer are written as fp16 by the GEMM
-      // D = 32: head w lives in 64-column box w / 2, in the upper or lower 64 bytes of its 128-byte swizzled rows;
-      // D = 64: head w is box w
-      const uint32_t box = D == 32 ? uint32_t(w >> 1) : uint32_t(w), in_row = D == 32 ? uint32_t(w & 1) * 64u : 0u;
-      const uint32_t k_off = box * (A3_KV / 2) + in_row;
-      const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
-      const uint64_t qd = make_sdesc(smem_u32(sQ) + box * (A3_Q / 2) + in_row, 16, 1024);
-      const uint64_t kd0 = make_sdesc(smem_u32(sK) + k_off, 16, 1024);
-      const uint64_t mxd0 = make_sdesc_noswizzle(smem_u32(sMext), 128, 256);
-      const uint64_t vd0 = make_sdesc(smem_u32(sV) + k_off, 16384, 1024);  // V is N-major: 16 keys = 2048 B
-      const uint32_t d_s = tmem_base + w * 64, d_o = tmem_base + A3_TM_O + w * D, a_p = tmem_base + A3_TM_P + w * 32;
-      uint64_t* my_sb = sb_full + w * 2;
-      const uint32_t my_bias = smem_u32(sBias) + w * A3_BS * A3_BT;
-      bool okay = true;
-      // next block whose logits are issued (one ahead of the softmax), tracked without divisions
-      uint32_t aj = 0, ait = 0;
-      int akb = 0;
-      auto issue_s = [&]() -> bool {
-        const uint32_t ks = aj & 1u;
-        if (akb == 0 && !mbar_wait(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
-        if (!mbar_wait(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
-        tc_fence_after();
-        if (leader) {
-          const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
-#pragma unroll
-          for (int j = 0; j < D / 16; ++j)  // 16 head-dimension columns = 32 B inside the swizzled row
-            umma_ss(d_s, qd + uint64_t(2 * j), kd + uint64_t(2 * j), idesc_s, j ? 1u : 0u);
-          umma_ss(d_s, e1d, mxd0 + uint64_t(ks * (2048 >> 4)), idesc_s, 1u);
-          umma_commit(&my_sb[ks]);  // ks = block & 1
-          umma_commit(&k_empty[ks]);
-          if (akb == KB - 1) umma_commit(q_empty);  // last use of this item's Q tile
+    } else if (warp == 7) {
+      // ------------------------------------------------------------------------------------------- TMA producer of V
+      if (lane == 0) {
+        uint32_t j = 0;
+        bool okay = true;
+        for (uint32_t it = 0; it < my_items && okay; ++it) {
+          int qt, hg, b;
+          decode(it, qt, hg, b);
+          for (int kb = 0; kb < KB; ++kb, ++j) {
+            const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
+            if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
+            mbar_arrive_expect_tx(&v_full[st], A3_KV);
+  #pragma unroll
+            for (int x = 0; x < 2; ++x) {
+              const int col = p.v_col0 + hg * 128 + x * 64;
+              if (p.transposed) tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, b, kb * 64);
+              else tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, kb * 64, b);
+            }
+          }
         }
-        ++aj;
-        if (++akb == KB) {
-          akb = 0;
-          ++ait;
+      }
+    } else if (warp <= NH) {
+      // ------------------------------------------------------------------------------------------- MMA issuer of head w
+      // The whole warp runs this code with identical values in every lane (waits included), and one elected lane issues
+      // the tensor-core and TMA instructions: descriptors and counters are warp-uniform, built once outside the loop.
+      {
+        const int w = warp - 1;
+        const bool leader = elect_one();
+        constexpr uint32_t idesc_s = make_idesc(128, 64);
+        constexpr uint32_t idesc_pv = make_idesc(128, D, 0, 1, 1);  // P and V are fp16 (V N-major): the v columns of the
+                                                                    // projection buffer are written as fp16 by the GEMM
+        // D = 32: head w lives in 64-column box w / 2, in the upper or lower 64 bytes of its 128-byte swizzled rows;
+        // D = 64: head w is box w
+        const uint32_t box = D == 32 ? uint32_t(w >> 1) : uint32_t(w), in_row = D == 32 ? uint32_t(w & 1) * 64u : 0u;
+        const uint32_t k_off = box * (A3_KV / 2) + in_row;
+        const uint64_t e1d = make_sdesc_noswizzle(smem_u32(sE1), 128, 256);
+        const uint64_t qd = make_sdesc(smem_u32(sQ) + box * (A3_Q / 2) + in_row, 16, 1024);
+        const uint64_t kd0 = make_sdesc(smem_u32(sK) + k_off, 16, 1024);
+        const uint64_t mxd0 = make_sdesc_noswizzle(smem_u32(sMext), 128, 256);
+        const uint64_t vd0 = make_sdesc(smem_u32(sV) + k_off, 16384, 1024);  // V is N-major: 16 keys = 2048 B
+        const uint32_t d_s = tmem_base + w * 64, d_o = tmem_base + A3_TM_O + w * D, a_p = tmem_base + A3_TM_P + w * 32;
+        uint64_t* my_sb = sb_full + w * 2;
+        const uint32_t my_bias = smem_u32(sBias) + w * A3_BS * A3_BT;
+        bool okay = true;
+        // next block whose logits are issued (one ahead of the softmax), tracked without divisions
+        uint32_t aj = 0, ait = 0;
+        int akb = 0;
+        auto issue_s = [&]() -> bool {
+          const uint32_t ks = aj & 1u;
+          if (akb == 0 && !mbar_wait(q_full, ait & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+          if (!mbar_wait(&k_full[ks], (aj >> 1) & 1u, ab, XF_ERR_WAIT_FULL)) return false;
+          tc_fence_after();
+          if (leader) {
+            const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
+  #pragma unroll
+            for (int j = 0; j < D / 16; ++j)  // 16 head-dimension columns = 32 B inside the swizzled row
+              umma_ss(d_s, qd + uint64_t(2 * j), kd + uint64_t(2 * j), idesc_s, j ? 1u : 0u);
+            umma_ss(d_s, e1d, mxd0 + uint64_t(ks * (2048 >> 4)), idesc_s, 1u);
+            umma_commit(&my_sb[ks]);  // ks = block & 1
+            umma_commit(&k_empty[ks]);
+            if (akb == KB - 1) umma_commit(q_empty);  // last use of this item's Q tile
+          }
+          ++aj;
+          if (++akb == KB) {
+            akb = 0;
+            ++ait;
+          }
+          return true;
+        };
+        // next bias tile to fetch: half bi of the CTA's block sequence = (item, key block, half)
+        uint32_t bi = 0, bslot = 0, bit = 0;
+        int bkey = 0, bqt, bhg, bb_;
+        decode(0, bqt, bhg, bb_);
+        const int key_end = KB * 64;
+        auto issue_bias = [&]() {
+          if (leader) {
+            uint64_t* bar = &my_sb[(bi >> 1) & 1u];  // the barrier of the block this half belongs to
+            mbar_arrive_expect_tx(bar, A3_BT);
+            asm volatile(
+                "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                ::"r"(my_bias + bslot * A3_BT), "l"(&tmb), "r"(smem_u32(bar)), "r"(bkey), "r"(bqt * 128), "r"(bhg * NH + w)
+                : "memory");
+          }
+          ++bi;
+          if (++bslot == A3_BS) bslot = 0;
+          bkey += 32;
+          if (bkey == key_end) {
+            bkey = 0;
+            ++bit;
+            decode(bit, bqt, bhg, bb_);
+          }
+        };
+        const uint32_t n_half = 2u * G;
+        while (bi < uint32_t(A3_BS) && bi < n_half) issue_bias();
+        if (G > 0) okay = issue_s();
+        int kb = 0;  // key block of block g within its item
+        for (uint32_t g = 0; g < G && okay; ++g) {
+          const uint32_t par = g & 1u, vs = g & 1u, vpar = (g >> 1) & 1u;
+          // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1
+          if (!mbar_wait(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+          if (g + 1 < G && !issue_s()) break;
+          // the bias tile of the block's first half has been used up
+          if (!mbar_wait(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+          if (bi < n_half) issue_bias();
+          const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
+          if (!mbar_wait(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
+          if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
+          tc_fence_after();
+          if (leader) {
+            const uint64_t vd = vd0 + uint64_t(vs * (A3_KV >> 4));
+  #pragma unroll
+            for (int ks = 0; ks < 4; ++ks)  // 16 keys = 2048 B of V = 8 columns of P; O accumulates over the item
+              umma_ts(d_o, a_p + ks * 8, vd + uint64_t(ks * (2048 >> 4)), idesc_pv, (kb | ks) ? 1u : 0u);
+            umma_commit(&pv_done[w]);
+            umma_commit(&v_empty[vs]);
+          }
+          if (bi < n_half) issue_bias();
+          if (++kb == KB) kb = 0;
         }
-        return true;
-      };
-      // next bias tile to fetch: half bi of the CTA's block sequence = (item, key block, half)
-      uint32_t bi = 0, bslot = 0, bit = 0;
-      int bkey = 0, bqt, bhg, bb_;
-      decode(0, bqt, bhg, bb_);
-      const int key_end = KB * 64;
-      auto issue_bias = [&]() {
-        if (leader) {
-          uint64_t* bar = &my_sb[(bi >> 1) & 1u];  // the barrier of the block this half belongs to
-          mbar_arrive_expect_tx(bar, A3_BT);
-          asm volatile(
-              "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-              ::"r"(my_bias + bslot * A3_BT), "l"(&tmb), "r"(smem_u32(bar)), "r"(bkey), "r"(bqt * 128), "r"(bhg * NH + w)
-              : "memory");
-        }
-        ++bi;
-        if (++bslot == A3_BS) bslot = 0;
-        bkey += 32;
-        if (bkey == key_end) {
-          bkey = 0;
-          ++bit;
-          decode(bit, bqt, bhg, bb_);
-        }
-      };
-      const uint32_t n_half = 2u * G;
-      while (bi < uint32_t(A3_BS) && bi < n_half) issue_bias();
-      if (G > 0) okay = issue_s();
-      int kb = 0;  // key block of block g within its item
-      for (uint32_t g = 0; g < G && okay; ++g) {
-        const uint32_t par = g & 1u, vs = g & 1u, vpar = (g >> 1) & 1u;
-        // the softmax warps hold S(g) in registers: the logits buffer is free for block g + 1
-        if (!mbar_wait(&s_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
-        if (g + 1 < G && !issue_s()) break;
-        // the bias tile of the block's first half has been used up
-        if (!mbar_wait(&b_free[w], par, ab, XF_ERR_WAIT_ATTN)) break;
-        if (bi < n_half) issue_bias();
-        const bool v_ready = mbar_test_wait(&v_full[vs], vpar);
-        if (!mbar_wait(&p_ready[w], par, ab, XF_ERR_WAIT_ATTN)) break;
-        if (!v_ready && !mbar_wait(&v_full[vs], vpar, ab, XF_ERR_WAIT_FULL)) break;
-        tc_fence_after();
-        if (leader) {
-          const uint64_t vd = vd0 + uint64_t(vs * (A3_KV >> 4));
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)  // 16 keys = 2048 B of V = 8 columns of P; O accumulates over the item
-            umma_ts(d_o, a_p + ks * 8, vd + uint64_t(ks * (2048 >> 4)), idesc_pv, (kb | ks) ? 1u : 0u);
-          umma_commit(&pv_done[w]);
-          umma_commit(&v_empty[vs]);
-        }
-        if (bi < n_half) issue_bias();
-        if (++kb == KB) kb = 0;
       }
     }
-  }
   } else {
     if constexpr (NH == 4) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(A3_REGS_SOFTMAX));
     // ------------------------------------------------------------------------------------------- softmax warps
