@@ -697,11 +697,13 @@ cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, long long row_s
       mean[u] = sm * (1.f / 128);
       rstd[u] = rsqrtf(fmaxf(sq * (1.f / 128) - mean[u] * mean[u], 0.f) + eps);
     }
+    // Every thread holds its values in registers and the statistics are exchanged: the tile's buffer is free.  The
+    // normalised tokens are staged there token-major, so that they leave as whole 256-byte rows (a thread's own 2 x 64
+    // bytes written straight to global memory use half of every 128-byte line they touch).
+    bf16 (*stage)[CMLN_PITCH] = tile;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const int j = j0 + 2 * tp + u;
-      if (j >= N) continue;
-      bf16* orow = out + ((long long)i * N + j) * 128 + part * 32;
+      bf16* srow = &stage[2 * tp + u][part * 32];
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) {
         float o[8];
@@ -716,8 +718,17 @@ cm_ln_kernel(const bf16* __restrict__ in, long long chan_stride, long long row_s
         uint4 w4;
         w4.x = pack_bf16x2(o[0], o[1]); w4.y = pack_bf16x2(o[2], o[3]);
         w4.z = pack_bf16x2(o[4], o[5]); w4.w = pack_bf16x2(o[6], o[7]);
-        *reinterpret_cast<uint4*>(orow + g8 * 8) = w4;
+        *reinterpret_cast<uint4*>(srow + g8 * 8) = w4;
       }
+    }
+    __syncthreads();
+    // 128 tokens x 16 pieces of 16 bytes: a warp writes two whole token rows per instruction
+    for (int idx = threadIdx.x; idx < CMLN_TOK * 16; idx += 256) {
+      const int tk = idx >> 4, piece = idx & 15;
+      const int j = j0 + tk;
+      if (j < N)
+        *reinterpret_cast<uint4*>(out + ((long long)i * N + j) * 128 + piece * 8) =
+            *reinterpret_cast<const uint4*>(&stage[tk][piece * 8]);
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
