@@ -356,9 +356,9 @@ def main():
 
     # ---- roofline of the dominant kernel + the TriMul contraction -----------------------------
     hbm, tf_burst, tf_sust, which = peaks()
-    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the one-kernel ncu captures summarised
+    # DRAM bytes per launch (read + write; for attention dram__bytes.sum.per_second x duration) from the one-kernel ncu captures summarised
     # under profiles/, taken at N = 1024; these kernels' traffic grows with N^2, so other sizes are scaled by (N / 1024)^2
-    ncu_traffic_n1024 = {"attention": 1.117e9 + 0.257e9, "trimul_contract": 0.537e9 + 0.235e9}
+    ncu_traffic_n1024 = {"attention": 1.370e9, "trimul_contract": 0.537e9 + 0.235e9}
     tnote = "bytes per launch (ncu, one launch at N=1024" + ("" if n == 1024 else ", scaled by N^2") + ")"
     top = max(per_kernel, key=lambda k: per_kernel[k]["ms_per_step"]) if per_kernel else None
 
