@@ -218,7 +218,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           decode(it, qt, hg, b);
           if (!mbar_wait(q_empty, (it & 1u) ^ 1u, ab, XF_ERR_WAIT_EMPTY)) break;
           mbar_arrive_expect_tx(q_full, A3_Q);
-  #pragma unroll
+#pragma unroll
           for (int x = 0; x < 2; ++x) {
             const int col = p.q_col0 + hg * 128 + x * 64;
             if (p.transposed) tma_load_3d(sQ + x * (A3_Q / 2), &tmq, q_full, col, b, qt * 128);
@@ -229,7 +229,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
             if (!mbar_wait(&k_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
             mbar_arrive_expect_tx(&k_full[st], A3_KV + 2048);
-  #pragma unroll
+#pragma unroll
             for (int x = 0; x < 2; ++x) {
               const int col = p.k_col0 + hg * 128 + x * 64;
               if (p.transposed) tma_load_3d(sK + st * A3_KV + x * (A3_KV / 2), &tmkv, &k_full[st], col, b, kb * 64);
@@ -251,7 +251,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
             const uint32_t st = j & 1u, par = ((j >> 1) & 1u) ^ 1u;
             if (!mbar_wait(&v_empty[st], par, ab, XF_ERR_WAIT_EMPTY)) { okay = false; break; }
             mbar_arrive_expect_tx(&v_full[st], A3_KV);
-  #pragma unroll
+#pragma unroll
             for (int x = 0; x < 2; ++x) {
               const int col = p.v_col0 + hg * 128 + x * 64;
               if (p.transposed) tma_load_3d(sV + st * A3_KV + x * (A3_KV / 2), &tmkv, &v_full[st], col, b, kb * 64);
@@ -293,7 +293,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           tc_fence_after();
           if (leader) {
             const uint64_t kd = kd0 + uint64_t(ks * (A3_KV >> 4));   // descriptor start address counts 16-byte units
-  #pragma unroll
+#pragma unroll
             for (int j = 0; j < D / 16; ++j)  // 16 head-dimension columns = 32 B inside the swizzled row
               umma_ss(d_s, qd + uint64_t(2 * j), kd + uint64_t(2 * j), idesc_s, j ? 1u : 0u);
             umma_ss(d_s, e1d, mxd0 + uint64_t(ks * (2048 >> 4)), idesc_s, 1u);
@@ -349,7 +349,7 @@ attn3_kernel(const __grid_constant__ CUtensorMap tmq, const __grid_constant__ CU
           tc_fence_after();
           if (leader) {
             const uint64_t vd = vd0 + uint64_t(vs * (A3_KV >> 4));
-  #pragma unroll
+#pragma unroll
             for (int ks = 0; ks < 4; ++ks)  // 16 keys = 2048 B of V = 8 columns of P; O accumulates over the item
               umma_ts(d_o, a_p + ks * 8, vd + uint64_t(ks * (2048 >> 4)), idesc_pv, (kb | ks) ? 1u : 0u);
             umma_commit(&pv_done[w]);
